@@ -1,0 +1,178 @@
+/*
+ * fa_b200.h — C ABI of libfa_b200.so, a Blackwell (sm_100a) exact-attention library.
+ *
+ * The library replaces the five entry points of the FlashAttention v2.3.3 extension module
+ * `flash_attn_2_cuda` (csrc/flash_attn/flash_api.cpp:1281-1288: fwd, varlen_fwd, bwd, varlen_bwd,
+ * fwd_kvcache).  Those entry points take torch tensors; this ABI takes what they boil down to:
+ * raw device pointers, element strides, sizes and scalars.  Allocation, shape checks that need
+ * tensor metadata, head-dim padding and RNG state stay in the host shim (python module
+ * `flash_attn_2_cuda` of this repository).
+ *
+ * Conventions (same as the reference, csrc/flash_attn/flash_api.cpp:21-119):
+ *   - q is (batch, seqlen_q, heads, head_dim), k/v are (batch, seqlen_k, heads_k, head_dim); only
+ *     the last dimension must be contiguous.  Strides are in ELEMENTS and 64-bit.
+ *   - varlen: tensors are (total_tokens, heads, head_dim) and cu_seqlens_* hold batch+1 int32
+ *     prefix sums on the device; batch strides are ignored.
+ *   - head_dim must be a multiple of 8 and <= 256 (the shim pads, flash_api.cpp:313-322).
+ *   - softmax_lse is fp32 (batch, heads, seqlen_q) [varlen: (batch, heads, max_seqlen_q)], natural
+ *     log of the row sum of exp(scale * q.k), +inf for a row with no visible key
+ *     (csrc/flash_attn/src/flash_fwd_kernel.h:505-516).
+ *   - masks are aligned to the bottom-right corner: key j is visible to query i iff
+ *       i + shift - window_left <= j <= i + shift + window_right,  shift = seqlen_k - seqlen_q
+ *     with a negative window meaning "unbounded on that side" (csrc/flash_attn/src/softmax.h:142-179).
+ *     `causal` is window_right = 0.
+ *   - every function enqueues work on `stream` and returns without synchronising; 0 = success,
+ *     otherwise fa_last_error() describes the failure (the shim raises RuntimeError, mirroring
+ *     TORCH_CHECK in the reference).
+ */
+#ifndef FA_B200_H_
+#define FA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* fa_stream_t; /* a cudaStream_t */
+
+enum { FA_DTYPE_FP16 = 0, FA_DTYPE_BF16 = 1 };
+
+/* One strided (batch, seq, head, dim) operand: element strides, dim stride is 1. */
+typedef struct FaTensor {
+  void* ptr;
+  int64_t stride_b; /* batch stride (ignored for varlen) */
+  int64_t stride_s; /* row (token) stride */
+  int64_t stride_h; /* head stride */
+} FaTensor;
+
+/* Forward.  Replaces mha_fwd (flash_api.cpp:248-424) and mha_varlen_fwd (flash_api.cpp:426-585). */
+typedef struct FaFwdArgs {
+  FaTensor q, k, v, out;
+  float* softmax_lse;       /* (batch, heads, lse_seqlen) fp32 */
+  int32_t lse_seqlen;       /* row pitch of softmax_lse: seqlen_q, or max_seqlen_q for varlen */
+  int32_t batch, seqlen_q, seqlen_k, heads, heads_k, head_dim;
+  int32_t dtype;            /* FA_DTYPE_* */
+  float softmax_scale;
+  int32_t window_left, window_right; /* < 0: unbounded */
+  /* varlen (both NULL for fixed-length batches); seqlen_q/seqlen_k are then the maxima */
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+  int32_t total_q, total_k; /* rows of the packed tensors (varlen only) */
+  /* per-batch key lengths that are NOT cumulative (KV cache, flash_api.cpp:1198-1206); may be NULL */
+  const int32_t* seqused_k;
+  int32_t seqused_k_extra;  /* added to every seqused_k entry (rows appended to the cache by this call) */
+  /* optional gather of the k/v batch index (cache_batch_idx, flash_api.cpp:1234-1240) */
+  const int32_t* kv_batch_idx;
+  /* dropout (flash_api.cpp:391-406).  p_dropout = probability of dropping. */
+  float p_dropout;
+  uint64_t rng_seed, rng_offset;
+  /* optional (batch, heads, sdmask_rows, sdmask_cols) tensor of q's dtype receiving the softmax
+     probabilities with the sign bit set where the entry was dropped (flash_api.cpp:351-354). */
+  void* s_dmask;
+  int32_t sdmask_rows, sdmask_cols;
+  /* split-KV (flash_api.cpp:373-389): num_splits <= 1 means one pass.  Workspaces are fp32:
+     lse_accum (num_splits, batch, heads, seqlen_q), out_accum (num_splits, batch, heads, seqlen_q, head_dim). */
+  int32_t num_splits;
+  float* lse_accum;
+  float* out_accum;
+  /* Mask shift override used by the context-parallel ring: when use_mask_shift != 0 the `shift`
+     of the mask rule above is mask_shift instead of seqlen_k - seqlen_q (no reference counterpart;
+     the reference has no ring attention). */
+  int32_t use_mask_shift;
+  int32_t mask_shift;
+} FaFwdArgs;
+
+/* Backward.  Replaces mha_bwd (flash_api.cpp:609-811) and mha_varlen_bwd (flash_api.cpp:813-1036),
+   i.e. the three launches dot_do_o -> dq_dk_dv -> convert_dq of
+   csrc/flash_attn/src/flash_bwd_launch_template.h:47-90. */
+typedef struct FaBwdArgs {
+  FaTensor q, k, v, out, dout, dq, dk, dv;
+  const float* softmax_lse; /* from the forward, same layout */
+  int32_t lse_seqlen;
+  float* softmax_d;         /* (batch, heads, d_seqlen) fp32 out: rowsum(dO * O) */
+  int32_t d_seqlen;         /* row pitch of softmax_d (seqlen_q rounded up to 128) */
+  float* dq_accum;          /* fp32 workspace, fa_bwd_workspace_bytes() bytes, need not be zeroed */
+  int32_t batch, seqlen_q, seqlen_k, heads, heads_k, head_dim;
+  int32_t dtype;
+  float softmax_scale;
+  int32_t window_left, window_right;
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+  int32_t total_q, total_k;
+  float p_dropout;
+  uint64_t rng_seed, rng_offset;
+  int32_t use_mask_shift;
+  int32_t mask_shift;
+  /* when non-zero dk/dv are ACCUMULATED into fp32 tensors dk_accum/dv_accum of shape
+     (batch|total_k, seqlen_k, heads_k, head_dim) instead of being stored (ring backward). */
+  int32_t accumulate_dkv;
+  float* dk_accum;
+  float* dv_accum;
+} FaBwdArgs;
+
+/* KV-cache decode.  Replaces mha_fwd_kvcache (flash_api.cpp:1038-1279). */
+typedef struct FaKvcacheArgs {
+  FaTensor q, kcache, vcache, out;
+  FaTensor knew, vnew;      /* ptr NULL when there is nothing to append */
+  float* softmax_lse;       /* (batch, heads, seqlen_q) */
+  int32_t batch, batch_cache, seqlen_q, seqlen_cache, seqlen_new, heads, heads_k, head_dim;
+  int32_t dtype;
+  float softmax_scale;
+  int32_t window_left, window_right;
+  const int32_t* cache_seqlens;   /* (batch) int32 or NULL (= seqlen_cache) */
+  const int32_t* cache_batch_idx; /* (batch) int32 or NULL */
+  const void* rotary_cos;         /* (seqlen_ro, rotary_dim/2) of q's dtype or NULL */
+  const void* rotary_sin;
+  int32_t rotary_dim, seqlen_ro, rotary_interleaved;
+  /* q rows of one KV head that were folded into the row dimension by the caller
+     (flash_api.cpp:1096-1104); rotary then uses one position for all rows. */
+  int32_t q_rows_share_position;
+  int32_t num_splits;             /* 0 = choose, 1 = none, <= 128 */
+  /* workspaces, fa_kvcache_workspace_bytes() */
+  float* lse_accum;
+  float* out_accum;
+  void* q_rotated;                /* scratch for rotated q when the generic path is taken, or NULL */
+} FaKvcacheArgs;
+
+/* flash_attn_2_cuda.fwd / varlen_fwd */
+int fa_fwd(const FaFwdArgs* args, fa_stream_t stream);
+/* flash_attn_2_cuda.bwd / varlen_bwd */
+int fa_bwd(const FaBwdArgs* args, fa_stream_t stream);
+/* flash_attn_2_cuda.fwd_kvcache */
+int fa_fwd_kvcache(const FaKvcacheArgs* args, fa_stream_t stream);
+
+/* Number of KV splits fa_fwd would like for these sizes (num_splits_heuristic, flash_api.cpp:206-246).
+   The caller sizes lse_accum/out_accum from it and passes it back in FaFwdArgs.num_splits. */
+int fa_fwd_num_splits(int32_t batch, int32_t heads, int32_t seqlen_q, int32_t seqlen_k, int32_t head_dim,
+                      int32_t num_sms);
+/* Splits and workspace sizes of fa_fwd_kvcache for these arguments (pointers may be NULL);
+   returns the number of splits that the call will use and stores the byte sizes. */
+int fa_kvcache_plan(const FaKvcacheArgs* args, int32_t num_sms, int64_t* lse_accum_bytes, int64_t* out_accum_bytes);
+/* Bytes of FaBwdArgs.dq_accum (dq_accum of flash_api.cpp:735-739, 950-961). */
+int64_t fa_bwd_workspace_bytes(int32_t batch, int32_t seqlen_q, int32_t heads, int32_t head_dim, int32_t total_q,
+                               int32_t is_varlen);
+
+/* Merge partial attention results by their log-sum-exp (combine_attn_seqk_parallel,
+   csrc/flash_attn/src/flash_fwd_kernel.h:1169-1327).  out_parts (n_parts, rows, head_dim) fp32 and
+   lse_parts (n_parts, rows) fp32 -> out (rows, head_dim) of `dtype` with row stride out_row_stride,
+   lse (rows) fp32. */
+int fa_combine(const float* out_parts, const float* lse_parts, void* out, float* lse, int32_t n_parts, int64_t rows,
+               int32_t head_dim, int64_t out_row_stride, int32_t dtype, fa_stream_t stream);
+
+/* sizeof() of the argument structs as compiled (0: FaTensor, 1: FaFwdArgs, 2: FaBwdArgs,
+   3: FaKvcacheArgs), so that a foreign-function binding can verify its own layout. */
+int fa_abi_struct_size(int32_t which);
+
+/* Message for the last non-zero status returned on this thread. */
+const char* fa_last_error(void);
+/* Compile-time facts: "sm_100a", kernel list, build flags. */
+const char* fa_build_info(void);
+/* Device-side status word of the tensor-core kernels: 0 = ok, otherwise the code of the first
+   bounded wait that gave up (the kernels never spin forever).  Synchronises the device. */
+int fa_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H_ */
