@@ -1,0 +1,322 @@
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" = one forward + backward of exact attention on the workload's batch.  Default workload:
+packed-QKV training shape, batch 16 x seqlen 2048 x 16 heads x head_dim 128, bf16, causal,
+dropout 0 (the shape of the reference's own sweep, benchmarks/benchmark_flash_attention.py:74-78).
+Metric: fwd+bwd TFLOPS/s with the reference's FLOP model (benchmarks/benchmark_flash_attention.py:27-30):
+fwd = 4*B*S^2*H*D (halved when causal), bwd = 2.5x fwd.
+
+N > 1 (torchrun, one rank per GPU): every rank runs the same per-GPU batch (independent
+(batch x head) units, no communication); value = total FLOPs of all ranks / max-over-ranks time.
+`--workload ring` shards ONE long sequence over the ranks with context-parallel ring attention.
+
+`--impl reference` times the reference's CPU attention (the fp32 oracle restatement of attention_ref)
+on the host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT in sys.path:
+    sys.path.remove(ROOT)
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (batch, seqlen, heads, heads_k, head_dim, causal, dtype)
+    "train_b16_s2048_h16_d128_causal": (16, 2048, 16, 16, 128, True, torch.bfloat16),
+    "train_b16_s2048_h16_d128": (16, 2048, 16, 16, 128, False, torch.bfloat16),
+    "train_b16_s2048_h32_d64_causal": (16, 2048, 32, 32, 64, True, torch.bfloat16),
+    "gqa_b1_s32768_h32_hk8_d128_causal": (1, 32768, 32, 8, 128, True, torch.bfloat16),
+}
+DEFAULT = "train_b16_s2048_h16_d128_causal"
+
+
+def fwd_flops(B, S, H, D, causal):
+    return 4.0 * B * S * S * H * D / (2.0 if causal else 1.0)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(source="measured", hbm_gbs=p["hbm_gbs"], tflops_burst=p["bf16_tflops"],
+                    tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]))
+    return dict(source="fallback", hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def cpu_attention_sample(D, S, causal, heads=1, repeats=1):
+    """fp32 oracle forward+backward on the host cores for `heads` (batch x head) units of length S."""
+    from oracle import attention_oracle as O
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(1, S, heads, D, generator=g).requires_grad_(True) for _ in range(3))
+    do = torch.randn(1, S, heads, D, generator=g)
+    best = None
+    for _ in range(repeats + 1):  # first pass warms the allocator
+        t0 = time.perf_counter()
+        out, _ = O.attention_oracle(q, k, v, causal=causal)
+        torch.autograd.grad(out, (q, k, v), do)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def run_reference(args, wl):
+    B, S, H, Hk, D, causal, dtype = WORKLOADS[wl]
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    units = 2  # (batch x head) units per step: a bounded sample of the B*H units of the workload
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt = cpu_attention_sample(D, S, causal, heads=units)
+        if i >= args.warmup:
+            times.append(dt)
+    t = sum(times) / len(times)
+    fl = 3.5 * fwd_flops(1, S, units, D, causal)
+    val = fl / t / 1e12
+    sample = "%d of %d (batch x head) units at full seqlen %d per step, fp32 attention_ref restatement, fwd+bwd" % (units, B * H, S)
+    print(json.dumps({
+        "impl": "reference", "metric": "attention fwd+bwd TFLOPS/s", "value": val, "unit": "TFLOPS/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOPS/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOPS/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.workload == "ring":
+        from flash_attention_b200 import ring_bench
+
+        return ring_bench.main(args)
+    wl = args.workload
+    if args.impl == "reference":
+        return run_reference(args, wl)
+
+    import flash_attention_b200 as fa
+    from flash_attention_b200 import _lib
+
+    B, S, H, Hk, D, causal, dtype = WORKLOADS[wl]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+    packed = H == Hk
+    if packed:
+        qkv = torch.randn(B, S, 3, H, D, device=dev, dtype=dtype, generator=g).requires_grad_(True)
+        inputs = (qkv,)
+    else:
+        q = torch.randn(B, S, H, D, device=dev, dtype=dtype, generator=g).requires_grad_(True)
+        k = torch.randn(B, S, Hk, D, device=dev, dtype=dtype, generator=g).requires_grad_(True)
+        v = torch.randn(B, S, Hk, D, device=dev, dtype=dtype, generator=g).requires_grad_(True)
+        inputs = (q, k, v)
+    dout = torch.randn(B, S, H, D, device=dev, dtype=dtype, generator=g)
+
+    def forward(inp):
+        if packed:
+            return fa.flash_attn_qkvpacked_func(inp[0], causal=causal)
+        return fa.flash_attn_func(inp[0], inp[1], inp[2], causal=causal)
+
+    def step(inp, do):
+        out = forward(inp)
+        return out, torch.autograd.grad(out, inp, do)
+
+    f_fwd = fwd_flops(B, S, H, D, causal)
+    f_step = 3.5 * f_fwd
+    for _ in range(max(3, args.warmup)):
+        step(inputs, dout)
+    # ---- timed region: K steps, device timed, max over ranks
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local) as clk:
+        ev0.record()
+        for _ in range(args.steps):
+            step(inputs, dout)
+        ev1.record()
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    ms_step = ms / args.steps
+    value = world * f_step / (ms_step * 1e-3) / 1e12
+
+    # ---- forward and backward timed separately (the kernels behind the roofline numbers)
+    def timed(fn, n):
+        a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(n):
+            fn()
+        b_.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b_) / n
+
+    n_sub = max(3, min(args.steps, 20))
+    with torch.no_grad():
+        ms_fwd = timed(lambda: forward(inputs), n_sub)
+    out = forward(inputs)
+    ms_bwd = timed(lambda: torch.autograd.grad(out, inputs, dout, retain_graph=True), n_sub)
+    pk = peaks()
+    tf_fwd = f_fwd / (ms_fwd * 1e-3) / 1e12
+    tf_bwd = 2.5 * f_fwd / (ms_bwd * 1e-3) / 1e12
+    # the backward main loop is the dominant kernel of a step (its launch also covers the two small
+    # bandwidth kernels before and after it, a few percent of the time: see profiles/)
+    roofline = {"bound": "tensor", "kernel": "backward (dq_dk_dv main loop + dot_do_o + convert_dq)",
+                "achieved": tf_bwd, "peak": pk["tflops_burst"], "unit": "TFLOP/s",
+                "frac": tf_bwd / pk["tflops_burst"], "traffic": None, "peak_source": pk["source"],
+                "forward": {"kernel": "fwd_tc_kernel", "achieved": tf_fwd, "frac": tf_fwd / pk["tflops_burst"],
+                            "frac_of_sustained": tf_fwd / pk["tflops_sustained"]},
+                "frac_of_sustained": tf_bwd / pk["tflops_sustained"]}
+
+    # ---- end to end: host (pinned) -> device copies of the step's inputs, device -> host read of a result
+    host_in = [x.detach().cpu().pin_memory() for x in inputs]
+    host_do = dout.cpu().pin_memory()
+    dev_in = [torch.empty_like(x).requires_grad_(True) for x in inputs]
+    dev_do = torch.empty_like(dout)
+    h2d = sum(x.numel() * x.element_size() for x in host_in) + host_do.numel() * host_do.element_size()
+    res_host = torch.empty(1, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        for d_, h_ in zip(dev_in, host_in):
+            d_.data.copy_(h_, non_blocking=True)
+        dev_do.copy_(host_do, non_blocking=True)
+        o, grads = step(tuple(dev_in), dev_do)
+        res_host.copy_(grads[0].flatten()[:1].float(), non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    n_e2e = max(3, min(args.steps, 10))
+    ev0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    ev1.record()
+    barrier()
+    ms_e2e = ev0.elapsed_time(ev1) / n_e2e
+    if dist is not None:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = t.item()
+    e2e_val = world * f_step / (ms_e2e * 1e-3) / 1e12
+    status = _lib.lib().fa_device_status()
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            units = 2
+            dt = cpu_attention_sample(D, S, causal, heads=units)
+            cpu = {"value": 3.5 * fwd_flops(1, S, units, D, causal) / dt / 1e12, "unit": "TFLOPS/s",
+                   "cores": os.cpu_count() or 1, "kind": "port",
+                   "sample": "%d of %d (batch x head) units at full seqlen %d, fp32 attention_ref restatement, fwd+bwd, %.1f s" % (units, B * H, S, dt)}
+        line = {
+            "metric": "attention fwd+bwd TFLOPS/s (bf16, d%d%s)" % (D, ", causal" if causal else ""),
+            "value": value, "unit": "TFLOPS/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if dtype == torch.bfloat16 else "fp16", "data": "synthetic",
+            "config": {"workload": wl, "batch_per_gpu": B, "seqlen": S, "heads": H, "heads_k": Hk, "head_dim": D,
+                       "causal": causal, "dropout_p": 0.0, "api": "flash_attn_qkvpacked_func" if packed else "flash_attn_func",
+                       "l2": "inputs (%.0f MiB per step) larger than L2" % (h2d / 2**20),
+                       "flop_model": "fwd 4*B*S^2*H*D%s, bwd 2.5x" % ("/2" if causal else "")},
+            "fwd_tflops": tf_fwd, "bwd_tflops": tf_bwd, "ms_fwd": ms_fwd, "ms_bwd": ms_bwd,
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_val, "unit": "TFLOPS/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                    "ms_per_step": ms_e2e},
+            "gpu_launches": args.steps * 4,
+            "clocks": clk.summary(), "device_status": status,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -26,7 +26,9 @@ int bwd_tc_main(const FaBwdArgs& a, cudaStream_t st);
 bool decode_eligible(const FaKvcacheArgs& a);
 int decode_plan(const FaKvcacheArgs& a, int num_sms);
 int decode_run(const FaKvcacheArgs& a, int num_splits, cudaStream_t st);
-int tc_device_status();
+int fwd_tc_status(bool clear);
+int decode_status(bool clear);
+int bwd_tc_status(bool clear);
 }  // namespace fa
 
 namespace fa_host {
@@ -92,7 +94,12 @@ const char* fa_build_info(void) {
          "fwd_generic(mma.sync),bwd_generic(mma.sync),combine,bwd_dot_do_o,bwd_convert_dq,kvcache_prep";
 }
 
-int fa_device_status(void) { return fa::tc_device_status(); }
+int fa_device_status(void) {
+  int s = fa::fwd_tc_status(true);
+  int d = fa::decode_status(true);
+  int w = fa::bwd_tc_status(true);
+  return s ? s : (w ? w : d);
+}
 
 int fa_abi_struct_size(int32_t which) {
   switch (which) {

@@ -1,6 +1,464 @@
+// Forward attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), head dim <= 128.
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row tiles that take turns on the
+// tensor pipe.  Warp roles (384 threads):
+//   warps 0-3   softmax of tile 0  (one thread per query row; tcgen05.ld 32x32b gives a thread its row)
+//   warps 4-7   softmax of tile 1
+//   warp  8     TMA producer: Q tiles once, then K(j), V(j), K(j+1), ... through a ring of slots
+//   warp  9     MMA issuer: one elected thread issues every tcgen05.mma
+//   warp  10    owns the TMEM allocation
+// TMEM columns (fp32): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).  P (16-bit) is
+// written over the first 64 columns of its S and fed to the PV MMA as the TMEM A operand.
+// MMA order  S0(0) S1(0) | PV0(j) S0(j+1) PV1(j) S1(j+1) | ...  so that while one tile is in its
+// softmax the other tile's two MMAs keep the tensor pipe busy.
+// Softmax works in the exp2 domain with a lazily updated reference maximum: O and the row sum are
+// only rescaled when the running maximum has grown by more than 2^8, which keeps the (expensive)
+// TMEM round trip of O off the common path; the final O/l and LSE do not depend on that choice.
+//
+// Same math as compute_attn_1rowblock (csrc/flash_attn/src/flash_fwd_kernel.h:74-580); mask rule of
+// csrc/flash_attn/src/softmax.h:142-179; O = 0 and LSE = +inf for rows without a visible key.
 #include "../fa_common.cuh"
+#include "ptx.cuh"
+#include "tma_host.cuh"
+
 namespace fa {
-bool fwd_tc_eligible(const FaFwdArgs&) { return false; }
-int fwd_tc(const FaFwdArgs&, cudaStream_t) { return 1; }
-int tc_device_status() { return 0; }
+
+using namespace ptx;
+
+namespace {
+
+constexpr int kBM = 128;  // rows per query tile
+constexpr int kBN = 128;  // keys per K/V tile
+constexpr int kChunkBytes = 128 * 128;  // [128 rows][64 x 16-bit]: one swizzled TMA box
+constexpr float kRescaleThreshold = 8.f;
+
+enum WaitCode { W_QFULL = 11, W_KVFULL = 12, W_KVEMPTY = 13, W_SFULL = 14, W_PFULL = 15, W_OFULL = 16 };
+
+template <int DH>
+struct Cfg {
+  static constexpr int NCHUNK = DH / 64;
+  static constexpr int TILE_BYTES = NCHUNK * kChunkBytes;
+  static constexpr int STAGES = DH == 128 ? 4 : 8;
+  static constexpr int SMEM_TILES = (2 + STAGES) * TILE_BYTES;
+  static constexpr int NBAR = 2 + 2 * STAGES + 6;
+  static constexpr int SMEM_BYTES = SMEM_TILES + NBAR * 8 + 16 + 1024;  // + barriers, tmem ptr/abort, align slack
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int COL_S0 = 0, COL_S1 = 128, COL_O0 = 256, COL_O1 = 256 + DH;
+};
+
+struct FwdTcParams {
+  CUtensorMap tq, tk, tv;
+  FaFwdArgs a;
+};
+
+template <typename T>
+struct Fmt;
+template <>
+struct Fmt<__half> {
+  static constexpr int kIdesc = 0;
+};
+template <>
+struct Fmt<__nv_bfloat16> {
+  static constexpr int kIdesc = 1;
+};
+
+template <typename T, int DH>
+__global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ FwdTcParams P) {
+  using C = Cfg<DH>;
+  const FaFwdArgs& a = P.a;
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  const uint32_t s_base = smem_addr(smem);
+  const uint32_t sQ = s_base;                        // 2 tiles
+  const uint32_t sKV = s_base + 2 * C::TILE_BYTES;   // STAGES slots
+  const uint32_t bar0 = s_base + C::SMEM_TILES;
+  auto bar_qfull = [&](int t) { return bar0 + 8 * t; };
+  auto bar_full = [&](int s) { return bar0 + 8 * (2 + s); };
+  auto bar_empty = [&](int s) { return bar0 + 8 * (2 + C::STAGES + s); };
+  auto bar_sfull = [&](int t) { return bar0 + 8 * (2 + 2 * C::STAGES + t); };
+  auto bar_pfull = [&](int t) { return bar0 + 8 * (2 + 2 * C::STAGES + 2 + t); };
+  auto bar_ofull = [&](int t) { return bar0 + 8 * (2 + 2 * C::STAGES + 4 + t); };
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + C::SMEM_TILES + C::NBAR * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::SMEM_TILES + C::NBAR * 8 + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, h = blockIdx.y, hk = h / (a.heads / a.heads_k);
+  const SeqInfo si = seq_info(a.cu_seqlens_q, a.cu_seqlens_k, nullptr, nullptr, a.seqlen_q, a.seqlen_k,
+                              a.use_mask_shift, a.mask_shift, b);
+  // heaviest blocks (largest row index under a causal mask) first
+  const int mblk = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int m_base = mblk * 2 * kBM;
+  if (m_base >= si.sq) return;  // uniform for the CTA
+
+  // per-tile key block ranges
+  int lo[2], hi[2];
+  bool active[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int m0 = m_base + t * kBM;
+    active[t] = m0 < si.sq;
+    if (active[t]) {
+      key_block_range(m0, kBM, kBN, si.sk, si.shift, a.window_left, a.window_right, lo[t], hi[t]);
+    } else {
+      lo[t] = hi[t] = 0;
+    }
+  }
+  int J_lo, J_hi;
+  if (hi[0] > lo[0] && hi[1] > lo[1]) {
+    J_lo = min(lo[0], lo[1]);
+    J_hi = max(hi[0], hi[1]);
+  } else if (hi[0] > lo[0]) {
+    J_lo = lo[0];
+    J_hi = hi[0];
+  } else {
+    J_lo = lo[1];
+    J_hi = hi[1];
+  }
+  const int nblk = J_hi - J_lo;  // may be 0
+
+  if (threadIdx.x == 0) {
+    *abort_flag = g_status;  // a failed earlier launch makes every later CTA bail out at its first wait
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar_qfull(t), 1);
+      mbar_init(bar_sfull(t), 1);
+      mbar_init(bar_pfull(t), 4);
+      mbar_init(bar_ofull(t), 1);
+    }
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_empty(s), 1);
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 10) {
+    tmem_alloc(smem_addr(const_cast<uint32_t*>(tmem_ptr_smem)), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_ptr_smem;
+
+  const float scale_log2 = a.softmax_scale * kLog2e;
+
+  if (warp < 8) {
+    // ------------------------------------------------------------------ softmax warpgroups
+    setmaxnreg_inc<216>();
+    const int t = warp >> 2;
+    const int row_in_tile = (warp & 3) * 32 + lane;
+    const int row = m_base + t * kBM + row_in_tile;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_off + (t ? C::COL_S1 : C::COL_S0);
+    const uint32_t tO = tmem + lane_off + (t ? C::COL_O1 : C::COL_O0);
+    float m_used = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    // first / last visible key of this row (inclusive)
+    int col_first = 0, col_last = si.sk - 1;
+    if (a.window_right >= 0) col_last = min(col_last, row + si.shift + a.window_right);
+    if (a.window_left >= 0) col_first = max(col_first, row + si.shift - a.window_left);
+    const int m0 = m_base + t * kBM;
+
+    for (int j = lo[t]; j < hi[t] && ok; ++j) {
+      const int it = j - lo[t];
+      ok = mbar_wait(bar_sfull(t), it & 1, W_SFULL, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t su[4][32];
+      tmem_ld32(tS + 0, su[0]);
+      tmem_ld32(tS + 32, su[1]);
+      tmem_ld32(tS + 64, su[2]);
+      tmem_ld32(tS + 96, su[3]);
+      tmem_wait_ld();
+#define S_AT(c) __uint_as_float(su[(c) >> 5][(c) & 31])
+      const int n0 = j * kBN;
+      const bool need_mask = (n0 + kBN - 1 >= si.sk) ||
+                             (a.window_right >= 0 && n0 + kBN - 1 > m0 + si.shift + a.window_right) ||
+                             (a.window_left >= 0 && n0 < m0 + kBM - 1 + si.shift - a.window_left);
+      if (need_mask) {
+        const int c_lo = col_first - n0, c_hi = col_last - n0;
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if (!(c >= c_lo && c <= c_hi)) su[c >> 5][c & 31] = 0xff800000u;  // -inf
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 128; c += 4) {
+        mx0 = fmaxf(mx0, S_AT(c));
+        mx1 = fmaxf(mx1, S_AT(c + 1));
+        mx2 = fmaxf(mx2, S_AT(c + 2));
+        mx3 = fmaxf(mx3, S_AT(c + 3));
+      }
+      const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+      const float m_cand = fmaxf(m_used, m_blk);
+      const bool grow = m_cand > m_used + kRescaleThreshold;  // also true when m_used is -inf and m_cand is finite
+      if (it > 0 && __any_sync(0xffffffffu, grow)) {
+        // O and l are relative to m_used: move them to the new reference
+        ok = mbar_wait(bar_ofull(t), (it - 1) & 1, W_OFULL, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const float f = grow ? fast_exp2(m_used - m_cand) : 1.f;
+#pragma unroll
+        for (int c0 = 0; c0 < DH; c0 += 32) {
+          uint32_t o[32];
+          tmem_ld32(tO + c0, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tmem_st32(tO + c0, o);
+        }
+        l_sum *= f;
+      }
+      if (grow) m_used = m_cand;
+      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+      uint32_t pu[2][32];
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 128; c += 2) {
+        float e0 = fast_exp2(fmaf(S_AT(c), scale_log2, neg_m));
+        float e1 = fast_exp2(fmaf(S_AT(c + 1), scale_log2, neg_m));
+        l0 += e0;
+        l1 += e1;
+        pu[c >> 6][(c >> 1) & 31] = Pack<T>::two(e0, e1);
+      }
+#undef S_AT
+      l_sum += l0 + l1;
+      tmem_st32(tS + 0, pu[0]);
+      tmem_st32(tS + 32, pu[1]);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pfull(t));
+    }
+
+    // ---- epilogue: O / l -> shared (swizzled) -> coalesced global stores; LSE
+    if (active[t]) {
+      const int n_it = hi[t] - lo[t];
+      bool have_o = n_it > 0 && ok;
+      if (have_o) {
+        ok = mbar_wait(bar_ofull(t), (n_it - 1) & 1, W_OFULL, abort_flag);
+        have_o = ok;
+        tc_fence_after();
+      }
+      if (ok) {
+        const bool empty = !(l_sum > 0.f) || m_used == -INFINITY;
+        const float inv = empty ? 0.f : 1.f / l_sum;
+        const float lse = empty ? INFINITY : (m_used + log2f(l_sum)) * kLn2;
+        if (row < si.sq) a.softmax_lse[((int64_t)b * a.heads + h) * a.lse_seqlen + row] = lse;
+        unsigned char* stage = smem + t * C::TILE_BYTES;  // the Q tile of this warpgroup is no longer read
+        constexpr int ROWB = DH * 2;
+#pragma unroll
+        for (int c0 = 0; c0 < DH; c0 += 32) {
+          uint32_t o[32];
+          if (have_o) {
+            tmem_ld32(tO + c0, o);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0u;
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {  // four 16-byte chunks of 8 elements
+            uint4 pk;
+            pk.x = Pack<T>::two(__uint_as_float(o[q4 * 8 + 0]) * inv, __uint_as_float(o[q4 * 8 + 1]) * inv);
+            pk.y = Pack<T>::two(__uint_as_float(o[q4 * 8 + 2]) * inv, __uint_as_float(o[q4 * 8 + 3]) * inv);
+            pk.z = Pack<T>::two(__uint_as_float(o[q4 * 8 + 4]) * inv, __uint_as_float(o[q4 * 8 + 5]) * inv);
+            pk.w = Pack<T>::two(__uint_as_float(o[q4 * 8 + 6]) * inv, __uint_as_float(o[q4 * 8 + 7]) * inv);
+            const int chunk = c0 / 8 + q4;
+            const int phys = (chunk & ~7) | ((chunk ^ row_in_tile) & 7);
+            *reinterpret_cast<uint4*>(stage + row_in_tile * ROWB + phys * 16) = pk;
+          }
+        }
+      }
+      named_bar_sync(1 + t, 128);
+      if (ok) {
+        constexpr int CPR = DH / 8;  // 16-byte chunks per row
+        const int tid = threadIdx.x & 127;
+        unsigned char* stage = smem + t * C::TILE_BYTES;
+        T* og = reinterpret_cast<T*>(a.out.ptr) + si.q_batch * a.out.stride_b + si.q_row0 * a.out.stride_s +
+                (int64_t)h * a.out.stride_h;
+#pragma unroll 4
+        for (int i = tid; i < kBM * CPR; i += 128) {
+          const int r = i / CPR, chunk = i % CPR;
+          const int grow_ = m0 + r;
+          if (grow_ < si.sq) {
+            const int phys = (chunk & ~7) | ((chunk ^ r) & 7);
+            uint4 v = *reinterpret_cast<const uint4*>(stage + r * (DH * 2) + phys * 16);
+            if (chunk * 8 < a.head_dim) *reinterpret_cast<uint4*>(og + (int64_t)grow_ * a.out.stride_s + chunk * 8) = v;
+          }
+        }
+      }
+    }
+  } else {
+    setmaxnreg_dec<64>();
+    if (warp == 8) {
+      // ---------------------------------------------------------------- TMA producer
+      if (lane == 0) {
+        prefetch_tensormap(&P.tq);
+        prefetch_tensormap(&P.tk);
+        prefetch_tensormap(&P.tv);
+        const int qrow = (int)si.q_row0 + m_base;
+        const int qb = (int)si.q_batch, kb = (int)si.k_batch;
+        for (int t = 0; t < 2; ++t) {
+          if (!active[t] || hi[t] <= lo[t]) continue;
+          mbar_expect_tx(bar_qfull(t), C::TILE_BYTES);
+          for (int c = 0; c < C::NCHUNK; ++c)
+            tma_load_4d(sQ + t * C::TILE_BYTES + c * kChunkBytes, &P.tq, bar_qfull(t), c * 64, qrow + t * kBM, h, qb);
+        }
+        bool ok = true;
+        for (int idx = 0; idx < 2 * nblk && ok; ++idx) {
+          const int slot = idx % C::STAGES, round = idx / C::STAGES;
+          ok = mbar_wait(bar_empty(slot), (round & 1) ^ 1, W_KVEMPTY, abort_flag);
+          if (!ok) break;
+          const int j = J_lo + (idx >> 1);
+          const CUtensorMap* tm = (idx & 1) ? &P.tv : &P.tk;
+          mbar_expect_tx(bar_full(slot), C::TILE_BYTES);
+          for (int c = 0; c < C::NCHUNK; ++c)
+            tma_load_4d(sKV + slot * C::TILE_BYTES + c * kChunkBytes, tm, bar_full(slot), c * 64,
+                        (int)si.k_row0 + j * kBN, hk, kb);
+        }
+      }
+    } else if (warp == 9) {
+      // ---------------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        constexpr uint32_t idesc_s = make_idesc(kBM, kBN, Fmt<T>::kIdesc, 0, 0);
+        constexpr uint32_t idesc_o = make_idesc(kBM, DH, Fmt<T>::kIdesc, 0, 1);
+        bool ok = true;
+        int p_iter[2] = {0, 0};  // softmax iterations consumed per tile
+        auto issue_s = [&](int t, int slot) {
+          const uint32_t d = tmem + (t ? C::COL_S1 : C::COL_S0);
+#pragma unroll
+          for (int kk = 0; kk < DH / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
+            const uint64_t ad = smem_desc_sw128(sQ + t * C::TILE_BYTES + off, 16, 1024);
+            const uint64_t bd = smem_desc_sw128(sKV + slot * C::TILE_BYTES + off, 16, 1024);
+            mma_ss(d, ad, bd, idesc_s, kk > 0);
+          }
+          tc_commit(bar_sfull(t));
+        };
+        auto issue_pv = [&](int t, int slot, bool first) {
+          const uint32_t d = tmem + (t ? C::COL_O1 : C::COL_O0);
+          const uint32_t pa = tmem + (t ? C::COL_S1 : C::COL_S0);
+#pragma unroll
+          for (int kk = 0; kk < kBN / 16; ++kk) {
+            const uint64_t bd = smem_desc_sw128(sKV + slot * C::TILE_BYTES + kk * 2048, kChunkBytes, 1024);
+            mma_ts(d, pa + kk * 8, bd, idesc_o, (!first) || kk > 0);
+          }
+          tc_commit(bar_ofull(t));
+        };
+        auto in_range = [&](int t, int j) { return j >= lo[t] && j < hi[t]; };
+        auto slot_of = [&](int idx) { return idx % C::STAGES; };
+        auto wait_full = [&](int idx) {
+          return mbar_wait(bar_full(slot_of(idx)), (idx / C::STAGES) & 1, W_KVFULL, abort_flag);
+        };
+        if (nblk > 0) {
+          for (int t = 0; t < 2 && ok; ++t)
+            if (hi[t] > lo[t]) ok = mbar_wait(bar_qfull(t), 0, W_QFULL, abort_flag);
+          // prologue: S_t(J_lo)
+          if (ok) ok = wait_full(0);
+          if (ok) {
+            tc_fence_after();
+            for (int t = 0; t < 2; ++t)
+              if (in_range(t, J_lo)) issue_s(t, slot_of(0));
+            tc_commit(bar_empty(slot_of(0)));
+          }
+          for (int j = J_lo; j < J_hi && ok; ++j) {
+            const int iv = 2 * (j - J_lo) + 1;  // ring index of V(j)
+            const int ik = iv + 1;              // ring index of K(j+1)
+            ok = wait_full(iv);
+            if (!ok) break;
+            const bool more = j + 1 < J_hi;
+            if (more) {
+              ok = wait_full(ik);
+              if (!ok) break;
+            }
+            tc_fence_after();
+            for (int t = 0; t < 2 && ok; ++t) {
+              if (in_range(t, j)) {
+                ok = mbar_wait(bar_pfull(t), p_iter[t] & 1, W_PFULL, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(t, slot_of(iv), j == lo[t]);
+                ++p_iter[t];
+              }
+              if (t == 1) tc_commit(bar_empty(slot_of(iv)));
+              if (more && in_range(t, j + 1)) issue_s(t, slot_of(ik));
+              if (more && t == 1) tc_commit(bar_empty(slot_of(ik)));
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (*abort_flag) {
+    // give copies that may still be in flight time to land before the shared memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) {
+    }
+    __syncthreads();
+  }
+  if (warp == 10) tmem_dealloc(tmem, C::TMEM_COLS);
 }
+
+template <typename T, int DH>
+int launch_fwd_tc(const FaFwdArgs& a, cudaStream_t st) {
+  using C = Cfg<DH>;
+  FwdTcParams P;
+  P.a = a;
+  const bool varlen = a.cu_seqlens_q != nullptr;
+  const int64_t q_rows = varlen ? a.total_q : a.seqlen_q, k_rows = varlen ? a.total_k : a.seqlen_k;
+  const int64_t nb = varlen ? 1 : a.batch;
+  if (make_tmap_4d(&P.tq, a.q, a.dtype, q_rows, a.heads, nb, a.head_dim, kBM)) return 1;
+  if (make_tmap_4d(&P.tk, a.k, a.dtype, k_rows, a.heads_k, nb, a.head_dim, kBN)) return 1;
+  if (make_tmap_4d(&P.tv, a.v, a.dtype, k_rows, a.heads_k, nb, a.head_dim, kBN)) return 1;
+  auto kern = fwd_tc_kernel<T, DH>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) {
+      fa_host::set_error("fwd_tc_kernel: cannot reserve %d bytes of shared memory: %s", C::SMEM_BYTES,
+                         cudaGetErrorString(cudaGetLastError()));
+      return 2;
+    }
+    attr_set = true;
+  }
+  dim3 grid((a.seqlen_q + 2 * kBM - 1) / (2 * kBM), a.heads, a.batch);
+  kern<<<grid, 384, C::SMEM_BYTES, st>>>(P);
+  return fa_host::check_launch("fwd_tc_kernel");
+}
+
+}  // namespace
+
+bool fwd_tc_eligible(const FaFwdArgs& a) {
+  if (a.head_dim > 128 || a.p_dropout > 0.f || a.s_dmask || a.num_splits > 1) return false;
+  if (a.seqused_k || a.kv_batch_idx) return false;
+  if (a.seqlen_k <= 0) return false;
+  if (!tma_compatible(a.q) || !tma_compatible(a.k) || !tma_compatible(a.v)) return false;
+  if ((reinterpret_cast<uintptr_t>(a.out.ptr) & 15) || a.out.stride_s % 8 || a.out.stride_h % 8 || a.out.stride_b % 8)
+    return false;
+  if (a.cu_seqlens_q && (a.total_q <= 0 || a.total_k <= 0)) return false;
+  return encode_tiled_fn() != nullptr;
+}
+
+int fwd_tc(const FaFwdArgs& a, cudaStream_t st) {
+  const bool bf = a.dtype == FA_DTYPE_BF16;
+  if (a.head_dim <= 64) return bf ? launch_fwd_tc<__nv_bfloat16, 64>(a, st) : launch_fwd_tc<__half, 64>(a, st);
+  return bf ? launch_fwd_tc<__nv_bfloat16, 128>(a, st) : launch_fwd_tc<__half, 128>(a, st);
+}
+
+int fwd_tc_status(bool clear) {
+  int v = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
+  if (clear && v) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_status, &z, sizeof(int));
+  }
+  return v;
+}
+
+}  // namespace fa

@@ -1,0 +1,218 @@
+"""Context-parallel ring attention: ONE long sequence sharded over the ranks of a process group.
+
+The reference has no multi-GPU attention (its kernels see the whole sequence of the local heads);
+this module adds the sequence-sharded case on top of the same kernels.  Rank r owns the rows
+[r*S/P, (r+1)*S/P) of q, k, v.  In step s it attends its queries to the K/V block that started on
+rank (r - s) mod P, while that block is already on its way to the next rank (NCCL send/recv over
+NVLink on a side stream, received into this GPU's own memory before any kernel reads it).
+Partial results are merged by their log-sum-exp, the same math as the split-KV combine
+(csrc/flash_attn/src/flash_fwd_kernel.h:1227-1298).  Masks of a step are expressed with the
+`mask_shift` field of the C ABI: shift = (global row of local q row 0) - (global row of block key 0).
+
+Backward runs a second ring in which each K/V block travels together with fp32 accumulators of
+its dK/dV; dQ stays local.  It uses the final (global) LSE and out of the forward.
+
+The per-block compute is pluggable (`block_ops`) so that the schedule and the merge can be tested on
+CPU ranks (gloo) with the oracle standing in for the CUDA kernels.
+"""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+
+# ------------------------------------------------------------------------------------------------
+class CudaBlockOps:
+    """Per-block forward/backward through the C ABI (fa_fwd / fa_bwd with a mask shift)."""
+
+    @staticmethod
+    def fwd(q, k, v, scale, window, shift):
+        from flash_attention_b200 import _lib
+        from flash_attention_b200._lib import FaFwdArgs, check, lib, ptr, tensor3
+
+        B, Sq, H, D = q.shape
+        Sk, Hk = k.shape[1], k.shape[2]
+        out = torch.empty_like(q)
+        lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+        a = FaFwdArgs()
+        a.q, a.k, a.v, a.out = tensor3(q), tensor3(k), tensor3(v), tensor3(out)
+        a.softmax_lse, a.lse_seqlen = ptr(lse), Sq
+        a.batch, a.seqlen_q, a.seqlen_k, a.heads, a.heads_k, a.head_dim = B, Sq, Sk, H, Hk, D
+        a.dtype = _lib.FA_DTYPE_BF16 if q.dtype == torch.bfloat16 else _lib.FA_DTYPE_FP16
+        a.softmax_scale = float(scale)
+        a.window_left, a.window_right = int(window[0]), int(window[1])
+        a.num_splits = 1
+        a.use_mask_shift, a.mask_shift = 1, int(shift)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
+        with torch.cuda.device(q.device):
+            check(lib().fa_fwd(ctypes.byref(a), stream), "ring block forward")
+        return out, lse
+
+    @staticmethod
+    def bwd(dout, q, k, v, out, lse, dk_acc, dv_acc, scale, window, shift):
+        """Returns this block's dq (q's dtype); adds the block's dk, dv into the fp32 accumulators."""
+        from flash_attention_b200 import _lib
+        from flash_attention_b200._lib import FaBwdArgs, check, lib, ptr, tensor3
+
+        B, Sq, H, D = q.shape
+        Sk, Hk = k.shape[1], k.shape[2]
+        dq = torch.empty_like(q)
+        d_seqlen = (Sq + 127) // 128 * 128
+        softmax_d = torch.empty((B, H, d_seqlen), dtype=torch.float32, device=q.device)
+        dq_accum = torch.empty(B * Sq * H * D, dtype=torch.float32, device=q.device)
+        a = FaBwdArgs()
+        a.q, a.k, a.v, a.out, a.dout, a.dq = (tensor3(x) for x in (q, k, v, out, dout, dq))
+        a.softmax_lse, a.lse_seqlen = ptr(lse), lse.shape[-1]
+        a.softmax_d, a.d_seqlen, a.dq_accum = ptr(softmax_d), d_seqlen, ptr(dq_accum)
+        a.batch, a.seqlen_q, a.seqlen_k, a.heads, a.heads_k, a.head_dim = B, Sq, Sk, H, Hk, D
+        a.dtype = _lib.FA_DTYPE_BF16 if q.dtype == torch.bfloat16 else _lib.FA_DTYPE_FP16
+        a.softmax_scale = float(scale)
+        a.window_left, a.window_right = int(window[0]), int(window[1])
+        a.use_mask_shift, a.mask_shift = 1, int(shift)
+        a.accumulate_dkv, a.dk_accum, a.dv_accum = 1, ptr(dk_acc), ptr(dv_acc)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
+        with torch.cuda.device(q.device):
+            check(lib().fa_bwd(ctypes.byref(a), stream), "ring block backward")
+        return dq
+
+
+# ------------------------------------------------------------------------------------------------
+def merge_partials(out_a, lse_a, out_b, lse_b):
+    """LSE-merge of two partial attention results.  out_*: (B, S, H, D) fp32, lse_*: (B, H, S) fp32
+    with +inf or -inf meaning "no visible key".  Returns fp32 (out, lse) with lse = -inf if empty."""
+    la = torch.where(torch.isinf(lse_a) & (lse_a > 0), torch.full_like(lse_a, float("-inf")), lse_a)
+    lb = torch.where(torch.isinf(lse_b) & (lse_b > 0), torch.full_like(lse_b, float("-inf")), lse_b)
+    lse = torch.logaddexp(la, lb)
+    wa = torch.exp(la - lse)
+    wb = torch.exp(lb - lse)
+    wa = torch.where(torch.isnan(wa), torch.zeros_like(wa), wa).transpose(1, 2).unsqueeze(-1)
+    wb = torch.where(torch.isnan(wb), torch.zeros_like(wb), wb).transpose(1, 2).unsqueeze(-1)
+    return out_a * wa + out_b * wb, lse
+
+
+def _normalize_window(causal, window_size):
+    wl, wr = int(window_size[0]), int(window_size[1])
+    if causal:
+        wr = 0
+    return wl, wr
+
+
+def block_visible(q0, nq, k0, nk, window):
+    """Does any (query, key) pair of the two global row ranges satisfy the window rule
+    key in [query - wl, query + wr]?  (negative = unbounded)"""
+    wl, wr = window
+    if wr >= 0 and k0 > q0 + nq - 1 + wr:
+        return False
+    if wl >= 0 and k0 + nk - 1 < q0 - wl:
+        return False
+    return True
+
+
+class _P2P:
+    """Exchange of a list of tensors around the ring: send to rank+1, receive from rank-1."""
+
+    def __init__(self, group):
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.next = dist.get_global_rank(group, (self.rank + 1) % self.world) if group is not None else (self.rank + 1) % self.world
+        self.prev = dist.get_global_rank(group, (self.rank - 1) % self.world) if group is not None else (self.rank - 1) % self.world
+
+    def start(self, send_tensors, recv_tensors):
+        ops = []
+        for s, r in zip(send_tensors, recv_tensors):
+            ops.append(dist.P2POp(dist.isend, s, self.next, group=self.group))
+            ops.append(dist.P2POp(dist.irecv, r, self.prev, group=self.group))
+        return dist.batch_isend_irecv(ops)
+
+    @staticmethod
+    def finish(reqs):
+        for r in reqs:
+            r.wait()
+
+
+def ring_forward(q, k, v, scale, causal, window_size, group=None, block_ops=CudaBlockOps):
+    """Forward of ring attention on this rank's shard. q: (B, S_loc, H, D); k, v: (B, S_loc, Hk, D).
+    Global sequence = concatenation of the shards in rank order.  Returns (out, lse) with lse fp32
+    (B, H, S_loc), +inf where a row sees no key."""
+    p2p = _P2P(group)
+    P, r = p2p.world, p2p.rank
+    S_loc = q.shape[1]
+    window = _normalize_window(causal, window_size)
+    k_cur, v_cur = k.contiguous(), v.contiguous()
+    out_acc = lse_acc = None
+    for s in range(P):
+        src = (r - s) % P
+        reqs = None
+        if s + 1 < P:
+            k_nxt, v_nxt = torch.empty_like(k_cur), torch.empty_like(v_cur)
+            reqs = p2p.start([k_cur, v_cur], [k_nxt, v_nxt])
+        if block_visible(r * S_loc, S_loc, src * S_loc, S_loc, window):
+            o, l = block_ops.fwd(q, k_cur, v_cur, scale, window, (r - src) * S_loc)
+            if out_acc is None:
+                out_acc, lse_acc = o.float(), torch.where(torch.isinf(l), torch.full_like(l, float("-inf")), l)
+            else:
+                out_acc, lse_acc = merge_partials(out_acc, lse_acc, o.float(), l)
+        if reqs is not None:
+            p2p.finish(reqs)
+            k_cur, v_cur = k_nxt, v_nxt
+    if out_acc is None:
+        out_acc = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        lse_acc = torch.full((q.shape[0], q.shape[2], S_loc), float("-inf"), device=q.device)
+    lse = torch.where(torch.isinf(lse_acc) & (lse_acc < 0), torch.full_like(lse_acc, float("inf")), lse_acc)
+    return out_acc.to(q.dtype), lse
+
+
+def ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group=None, block_ops=CudaBlockOps):
+    """Backward of ring attention.  Returns (dq, dk, dv) of this rank's shards."""
+    p2p = _P2P(group)
+    P, r = p2p.world, p2p.rank
+    S_loc = q.shape[1]
+    window = _normalize_window(causal, window_size)
+    k_cur, v_cur = k.contiguous(), v.contiguous()
+    dk_cur = torch.zeros(k.shape, dtype=torch.float32, device=k.device)
+    dv_cur = torch.zeros(v.shape, dtype=torch.float32, device=v.device)
+    dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    dout = dout.contiguous()
+    for s in range(P):
+        src = (r - s) % P
+        reqs = None
+        if s + 1 < P:  # K/V of the next step can already travel; dK/dV follow after this step's compute
+            k_nxt, v_nxt = torch.empty_like(k_cur), torch.empty_like(v_cur)
+            reqs = p2p.start([k_cur, v_cur], [k_nxt, v_nxt])
+        if block_visible(r * S_loc, S_loc, src * S_loc, S_loc, window):
+            dq += block_ops.bwd(dout, q, k_cur, v_cur, out, lse, dk_cur, dv_cur, scale, window, (r - src) * S_loc).float()
+        if reqs is not None:
+            p2p.finish(reqs)
+        # pass the gradient accumulators of this block on (after P hops they are back home)
+        dk_nxt, dv_nxt = torch.empty_like(dk_cur), torch.empty_like(dv_cur)
+        p2p.finish(p2p.start([dk_cur, dv_cur], [dk_nxt, dv_nxt]))
+        dk_cur, dv_cur = dk_nxt, dv_nxt
+        if s + 1 < P:
+            k_cur, v_cur = k_nxt, v_nxt
+    return dq.to(q.dtype), dk_cur.to(k.dtype), dv_cur.to(v.dtype)
+
+
+class RingAttnFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, softmax_scale, causal, window_size, group, block_ops):
+        if softmax_scale is None:
+            softmax_scale = q.shape[-1] ** (-0.5)
+        out, lse = ring_forward(q, k, v, softmax_scale, causal, window_size, group, block_ops)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.cfg = (softmax_scale, causal, window_size, group, block_ops)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        scale, causal, window_size, group, block_ops = ctx.cfg
+        dq, dk, dv = ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group, block_ops)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def ring_flash_attn_func(q, k, v, softmax_scale=None, causal=False, window_size=(-1, -1), group=None,
+                         block_ops=CudaBlockOps):
+    """Attention over a sequence that is sharded across the ranks of `group` (contiguous shards in
+    rank order).  Same semantics as flash_attn_func on the gathered sequence (seqlen_q == seqlen_k)."""
+    return RingAttnFunc.apply(q, k, v, softmax_scale, causal, tuple(window_size), group, block_ops)

@@ -1,0 +1,111 @@
+"""CPU-only checks of the boundary: the shared library loads, exports every symbol that
+include/fa_b200.h declares, agrees with the ctypes layout, validates arguments before any launch,
+and the drop-in module has the five entry points of the reference's extension."""
+import ctypes
+import inspect
+import os
+import re
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from flash_attention_b200.csrc import build as b
+
+    b.build()
+    from flash_attention_b200 import _lib
+
+    return _lib.lib()
+
+
+def test_every_declared_symbol_is_exported(lib):
+    header = open(os.path.join(ROOT, "include", "fa_b200.h")).read()
+    names = set(re.findall(r"^(?:int|int64_t|const char\*)\s+(fa_\w+)\s*\(", header, flags=re.M))
+    from flash_attention_b200 import _lib
+
+    assert names == set(_lib.EXPORTS), names ^ set(_lib.EXPORTS)
+    for n in names:
+        assert getattr(lib, n) is not None
+
+
+def test_struct_layouts_match(lib):
+    from flash_attention_b200 import _lib
+
+    for which, st in enumerate((_lib.FaTensor, _lib.FaFwdArgs, _lib.FaBwdArgs, _lib.FaKvcacheArgs)):
+        assert lib.fa_abi_struct_size(which) == ctypes.sizeof(st)
+    assert lib.fa_abi_struct_size(99) == -1
+    assert b"sm_100a" in lib.fa_build_info()
+
+
+def test_argument_validation_happens_before_launch(lib):
+    from flash_attention_b200 import _lib
+
+    a = _lib.FaFwdArgs()
+    a.batch, a.seqlen_q, a.seqlen_k, a.heads, a.heads_k, a.head_dim, a.dtype = 1, 8, 8, 4, 3, 64, 1
+    assert lib.fa_fwd(ctypes.byref(a), None) != 0
+    assert b"heads" in lib.fa_last_error()
+    a.heads_k, a.head_dim = 4, 260
+    assert lib.fa_fwd(ctypes.byref(a), None) != 0
+    assert b"256" in lib.fa_last_error()
+    a.head_dim = 60
+    assert lib.fa_fwd(ctypes.byref(a), None) != 0
+    assert b"multiple of 8" in lib.fa_last_error()
+    a.head_dim = 64
+    assert lib.fa_fwd(ctypes.byref(a), None) != 0  # null q pointer
+    assert b"null" in lib.fa_last_error()
+    k = _lib.FaKvcacheArgs()
+    k.batch, k.batch_cache, k.seqlen_q, k.seqlen_cache, k.heads, k.heads_k, k.head_dim, k.dtype = 1, 1, 1, 16, 4, 4, 64, 0
+    k.num_splits = 200
+    assert lib.fa_kvcache_plan(ctypes.byref(k), 148, None, None) < 0
+    assert b"num_splits" in lib.fa_last_error()
+
+
+def test_split_heuristic_matches_reference_rules(lib):
+    # flash_api.cpp:206-246: no split once 80 % of the SMs are covered; never more splits than key blocks
+    assert lib.fa_fwd_num_splits(16, 16, 2048, 2048, 128, 148) == 1
+    assert lib.fa_fwd_num_splits(1, 2, 64, 64, 128, 148) == 1
+    s = lib.fa_fwd_num_splits(1, 2, 64, 8192, 128, 148)
+    assert 1 < s <= 128
+    assert lib.fa_bwd_workspace_bytes(2, 100, 4, 64, 0, 0) == 2 * 100 * 4 * 64 * 4
+    assert lib.fa_bwd_workspace_bytes(2, 100, 4, 64, 150, 1) == 150 * 4 * 64 * 4
+
+
+def test_dropin_module_has_the_reference_entry_points():
+    import flash_attn_2_cuda as ext
+
+    assert os.path.dirname(os.path.abspath(ext.__file__)).startswith(ROOT), "an unrelated flash_attn_2_cuda shadows the shim"
+    # positional arities of csrc/flash_attn/flash_api.cpp:248-259, 426-442, 609-625, 813-834, 1038-1055
+    want = {"fwd": 11, "varlen_fwd": 16, "bwd": 16, "varlen_bwd": 21, "fwd_kvcache": 16}
+    for name, n in want.items():
+        assert len(inspect.signature(getattr(ext, name)).parameters) == n, name
+
+
+def test_shim_raises_runtime_error_like_torch_check():
+    import flash_attn_2_cuda as ext
+
+    q = torch.zeros(1, 4, 2, 16, dtype=torch.float32)
+    with pytest.raises(RuntimeError, match="fp16 and bf16"):
+        ext.fwd(q, q, q, None, 0.0, 1.0, False, -1, -1, False, None)
+    q = q.half()
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ext.fwd(q, q, q, None, 0.0, 1.0, False, -1, -1, False, None)
+
+
+@pytest.mark.skipif(not os.path.exists("/root/reference/flash_attn/flash_attn_interface.py"), reason="reference tree not present")
+def test_unmodified_reference_interface_binds_to_the_shim():
+    # the reference's python API file, loaded as is, must find everything it calls in our module
+    import importlib.util
+
+    import flash_attn_2_cuda as ext
+
+    spec = importlib.util.spec_from_file_location("ref_iface", "/root/reference/flash_attn/flash_attn_interface.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.flash_attn_cuda is ext
+    for fn in ("flash_attn_func", "flash_attn_qkvpacked_func", "flash_attn_varlen_func", "flash_attn_with_kvcache"):
+        assert callable(getattr(mod, fn))
