@@ -150,6 +150,102 @@ def run_reference(args, wl):
     }))
 
 
+def run_decode(args):
+    """KV-cache decode step: batch 64 (per GPU), 32 query heads, 8 KV heads, head_dim 128, bf16 cache of
+    capacity 32768 filled N(0,1), cache_seqlens uniform in [1024, 32767], one new token appended
+    in-kernel with NeoX rotary.  Metric: GB/s over the K and V rows actually attended to."""
+    import flash_attention_b200 as fa
+    from flash_attention_b200 import _lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    B, cap, H, Hk, D = 64, 32768, 32, 8, 128
+    g = torch.Generator(device=dev).manual_seed(4 + rank)
+    kc = torch.randn(B, cap, Hk, D, device=dev, dtype=torch.bfloat16, generator=g)
+    vc = torch.randn(B, cap, Hk, D, device=dev, dtype=torch.bfloat16, generator=g)
+    lens = torch.randint(1024, 32768, (B,), device=dev, generator=g).to(torch.int32)
+    q = torch.randn(B, 1, H, D, device=dev, dtype=torch.bfloat16, generator=g)
+    kn = torch.randn(B, 1, Hk, D, device=dev, dtype=torch.bfloat16, generator=g)
+    vn = torch.randn(B, 1, Hk, D, device=dev, dtype=torch.bfloat16, generator=g)
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2, device=dev).float() / D))
+    fr = torch.outer(torch.arange(cap, device=dev).float(), inv)
+    cos, sin = torch.cos(fr).bfloat16(), torch.sin(fr).bfloat16()
+    nbytes = float((lens.long() + 1).sum().item()) * Hk * D * 2 * 2
+
+    def step():
+        return fa.flash_attn_with_kvcache(q, kc, vc, kn, vn, cos, sin, lens, causal=True, rotary_interleaved=False)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local) as clk:
+        ev0.record()
+        for _ in range(args.steps):
+            step()  # the 8 GiB cache is far larger than L2: every step streams from HBM
+        ev1.record()
+        barrier()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    gbs = world * nbytes / (ms * 1e-3) / 1e9
+    # end to end: the per-step host inputs are the new token's q/k/v and the lengths; the cache is device state
+    hq, hk_, hv, hl = (x.cpu().pin_memory() for x in (q, kn, vn, lens))
+    out_host = torch.empty((B, 1, H, D), dtype=torch.bfloat16).pin_memory()
+
+    def e2e():
+        q.copy_(hq, non_blocking=True)
+        kn.copy_(hk_, non_blocking=True)
+        vn.copy_(hv, non_blocking=True)
+        lens.copy_(hl, non_blocking=True)
+        out_host.copy_(step(), non_blocking=True)
+
+    e2e()
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        e2e()
+    ev1.record()
+    barrier()
+    ms_e2e = ev0.elapsed_time(ev1) / args.steps
+    pk = peaks()
+    status = _lib.lib().fa_device_status()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "decode KV-cache GB/s (bf16, d128, split-KV)", "value": gbs, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "decode_b64_hq32_hk8_d128_cap32768", "batch_per_gpu": B, "cache_capacity": cap,
+                       "cache_seqlens": "uniform [1024, 32767]", "new_tokens": 1, "rotary": "neox, dim 128, base 10000",
+                       "l2": "8 GiB cache per GPU, larger than L2", "bytes_model": "sum_b (L_b + 1) * 8 * 128 * 2 B * 2"},
+            "roofline": {"bound": "hbm", "kernel": "decode_kernel (+ combine_kernel)", "achieved": gbs / world,
+                         "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / world / pk["hbm_gbs"], "traffic": None,
+                         "peak_source": pk["source"]},
+            "cpu_baseline": None,
+            "e2e": {"value": world * nbytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": sum(x.numel() * x.element_size() for x in (hq, hk_, hv, hl)),
+                    "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": ms_e2e},
+            "gpu_launches": args.steps * 2, "clocks": clk.summary(), "device_status": status,
+        }))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -163,6 +259,8 @@ def main():
         from flash_attention_b200 import ring_bench
 
         return ring_bench.main(args)
+    if args.workload == "decode":
+        return run_decode(args)
     wl = args.workload
     if args.impl == "reference":
         return run_reference(args, wl)
