@@ -11,8 +11,9 @@
 
 namespace fa {
 int fwd_generic(const FaFwdArgs& a, cudaStream_t st);
-int bwd_pre(const FaBwdArgs& a, cudaStream_t st);
+int bwd_pre(const FaBwdArgs& a, int zero_dq, cudaStream_t st);
 int bwd_post(const FaBwdArgs& a, cudaStream_t st);
+int bwd_post_blocked(const FaBwdArgs& a, int dhp, cudaStream_t st);
 int bwd_generic_main(const FaBwdArgs& a, cudaStream_t st);
 int combine(const float* out_parts, const float* lse_parts, const FaTensor& out, float* lse, int lse_pitch, int n_parts,
             int B, int H, int S, int D, int dtype, cudaStream_t st);
@@ -147,8 +148,14 @@ int fa_fwd_num_splits(int32_t batch, int32_t heads, int32_t seqlen_q, int32_t se
 
 int64_t fa_bwd_workspace_bytes(int32_t batch, int32_t seqlen_q, int32_t heads, int32_t head_dim, int32_t total_q,
                                int32_t is_varlen) {
+  // the larger of the two layouts the kernels may use: plain rows (any-shape kernel) and 128-row
+  // blocks of the padded head dim (tensor-core kernel, fa_common.cuh: dq_blocked_offset)
   int64_t rows = is_varlen ? (int64_t)total_q : (int64_t)batch * seqlen_q;
-  return rows * heads * head_dim * (int64_t)sizeof(float);
+  int64_t plain = rows * heads * head_dim * (int64_t)sizeof(float);
+  int64_t dhp = head_dim <= 64 ? 64 : (head_dim <= 128 ? 128 : head_dim);
+  int64_t units = is_varlen ? (int64_t)heads : (int64_t)batch * heads;
+  int64_t blocked = units * fa::dq_blocks_per_unit(is_varlen != 0, seqlen_q, total_q, batch) * 128 * dhp * (int64_t)sizeof(float);
+  return plain > blocked ? plain : blocked;
 }
 
 int fa_fwd(const FaFwdArgs* a, fa_stream_t stream) {
@@ -196,13 +203,27 @@ int fa_bwd(const FaBwdArgs* a, fa_stream_t stream) {
   FA_REQUIRE(a->p_dropout >= 0.f && a->p_dropout < 1.f, "p_dropout must be in [0, 1)");
   FA_REQUIRE(a->d_seqlen >= a->seqlen_q, "softmax_d row pitch is smaller than seqlen_q");
   if (a->seqlen_q == 0 || a->batch == 0) return 0;
-  int rc = fa::bwd_pre(*a, st);
+  const bool tc = a->seqlen_k > 0 && !fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::bwd_tc_eligible(*a);
+  const int dhp = a->head_dim <= 64 ? 64 : 128;
+  if (tc) {
+    // the tensor-core kernel adds whole 128-row blocks into a blocked accumulator: clear all of it
+    const bool varlen = a->cu_seqlens_q != nullptr;
+    const int64_t units = varlen ? (int64_t)a->heads : (int64_t)a->batch * a->heads;
+    const int64_t bytes = units * fa::dq_blocks_per_unit(varlen, a->seqlen_q, a->total_q, a->batch) * 128 * dhp * (int64_t)sizeof(float);
+    if (cudaMemsetAsync(a->dq_accum, 0, (size_t)bytes, st) != cudaSuccess) {
+      fa_host::set_error("clearing dq_accum failed: %s", cudaGetErrorString(cudaGetLastError()));
+      return 2;
+    }
+  }
+  int rc = fa::bwd_pre(*a, tc ? 0 : 1, st);
   if (rc) return rc;
+  if (tc) {
+    rc = fa::bwd_tc_main(*a, st);
+    if (rc) return rc;
+    return fa::bwd_post_blocked(*a, dhp, st);
+  }
   if (a->seqlen_k > 0) {
-    if (!fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::bwd_tc_eligible(*a))
-      rc = fa::bwd_tc_main(*a, st);
-    else
-      rc = fa::bwd_generic_main(*a, st);
+    rc = fa::bwd_generic_main(*a, st);
     if (rc) return rc;
   }
   return fa::bwd_post(*a, st);

@@ -18,8 +18,9 @@ namespace fa {
 
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(128) bwd_dot_do_o_kernel(const __grid_constant__ FaBwdArgs p) {
-  // one warp per query row; grid (ceil(max_sq/4), heads, batch)
+__global__ void __launch_bounds__(128) bwd_dot_do_o_kernel(const __grid_constant__ FaBwdArgs p, const int zero_dq) {
+  // one warp per query row; grid (ceil(max_sq/4), heads, batch).  zero_dq = 0 when the accumulator is
+  // the blocked one of the tensor-core path, which the host clears with a memset.
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int h = blockIdx.y, b = blockIdx.z;
@@ -45,8 +46,10 @@ __global__ void __launch_bounds__(128) bwd_dot_do_o_kernel(const __grid_constant
     acc += Pack<T>::lo(a.y) * Pack<T>::lo(d.y) + Pack<T>::hi(a.y) * Pack<T>::hi(d.y);
     acc += Pack<T>::lo(a.z) * Pack<T>::lo(d.z) + Pack<T>::hi(a.z) * Pack<T>::hi(d.z);
     acc += Pack<T>::lo(a.w) * Pack<T>::lo(d.w) + Pack<T>::hi(a.w) * Pack<T>::hi(d.w);
-    *reinterpret_cast<float4*>(dqa + c) = make_float4(0.f, 0.f, 0.f, 0.f);
-    *reinterpret_cast<float4*>(dqa + c + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (zero_dq) {
+      *reinterpret_cast<float4*>(dqa + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(dqa + c + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -69,6 +72,33 @@ __global__ void __launch_bounds__(128) bwd_convert_dq_kernel(const __grid_consta
   for (int c = lane * 8; c < D; c += 256) {
     float4 x = *reinterpret_cast<const float4*>(dqa + c);
     float4 y = *reinterpret_cast<const float4*>(dqa + c + 4);
+    uint4 o;
+    o.x = Pack<T>::two(x.x * sc, x.y * sc);
+    o.y = Pack<T>::two(x.z * sc, x.w * sc);
+    o.z = Pack<T>::two(y.x * sc, y.y * sc);
+    o.w = Pack<T>::two(y.z * sc, y.w * sc);
+    *reinterpret_cast<uint4*>(dq + c) = o;
+  }
+}
+
+// dQ = cast(dq_accum * softmax_scale) from the BLOCKED accumulator of the tensor-core backward
+// (layout: dq_blocked_offset in fa_common.cuh).  One thread per query row of a 128-row block, so
+// that a warp's loads of one 4-column chunk are 512 contiguous bytes.  grid (blocks, heads, batch).
+template <typename T>
+__global__ void __launch_bounds__(128) bwd_convert_dq_blocked_kernel(const __grid_constant__ FaBwdArgs p, const int dhp,
+                                                                     const int blocks_per_unit) {
+  const int r = threadIdx.x, mblk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const SeqInfo si = seq_info(p.cu_seqlens_q, p.cu_seqlens_k, nullptr, nullptr, p.seqlen_q, p.seqlen_k,
+                              p.use_mask_shift, p.mask_shift, b);
+  const int row = mblk * 128 + r;
+  if (row >= si.sq) return;
+  const int64_t blk = dq_block_index(p.cu_seqlens_q != nullptr, b, h, p.heads, (int)si.q_row0, blocks_per_unit) + mblk;
+  T* dq = reinterpret_cast<T*>(p.dq.ptr) + si.q_batch * p.dq.stride_b + (si.q_row0 + row) * p.dq.stride_s +
+          (int64_t)h * p.dq.stride_h;
+  const float sc = p.softmax_scale;
+  for (int c = 0; c < p.head_dim; c += 8) {
+    const float4 x = *reinterpret_cast<const float4*>(p.dq_accum + dq_blocked_offset(blk, r, c, dhp));
+    const float4 y = *reinterpret_cast<const float4*>(p.dq_accum + dq_blocked_offset(blk, r, c + 4, dhp));
     uint4 o;
     o.x = Pack<T>::two(x.x * sc, x.y * sc);
     o.y = Pack<T>::two(x.z * sc, x.w * sc);
@@ -330,10 +360,10 @@ static int launch_bwd_generic(const FaBwdArgs& a, cudaStream_t st) {
 }
 
 template <typename T>
-int bwd_pre_t(const FaBwdArgs& a, cudaStream_t st) {
+int bwd_pre_t(const FaBwdArgs& a, int zero_dq, cudaStream_t st) {
   int rows = a.d_seqlen > a.seqlen_q ? a.d_seqlen : a.seqlen_q;
   dim3 grid((rows + 3) / 4, a.heads, a.batch);
-  bwd_dot_do_o_kernel<T><<<grid, 128, 0, st>>>(a);
+  bwd_dot_do_o_kernel<T><<<grid, 128, 0, st>>>(a, zero_dq);
   return fa_host::check_launch("bwd_dot_do_o_kernel");
 }
 template <typename T>
@@ -343,8 +373,17 @@ int bwd_post_t(const FaBwdArgs& a, cudaStream_t st) {
   return fa_host::check_launch("bwd_convert_dq_kernel");
 }
 
-int bwd_pre(const FaBwdArgs& a, cudaStream_t st) {
-  return a.dtype == FA_DTYPE_BF16 ? bwd_pre_t<__nv_bfloat16>(a, st) : bwd_pre_t<__half>(a, st);
+int bwd_pre(const FaBwdArgs& a, int zero_dq, cudaStream_t st) {
+  return a.dtype == FA_DTYPE_BF16 ? bwd_pre_t<__nv_bfloat16>(a, zero_dq, st) : bwd_pre_t<__half>(a, zero_dq, st);
+}
+int bwd_post_blocked(const FaBwdArgs& a, int dhp, cudaStream_t st) {
+  const int bpu = dq_blocks_per_unit(a.cu_seqlens_q != nullptr, a.seqlen_q, a.total_q, a.batch);
+  dim3 grid((a.seqlen_q + 127) / 128, a.heads, a.batch);
+  if (a.dtype == FA_DTYPE_BF16)
+    bwd_convert_dq_blocked_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(a, dhp, bpu);
+  else
+    bwd_convert_dq_blocked_kernel<__half><<<grid, 128, 0, st>>>(a, dhp, bpu);
+  return fa_host::check_launch("bwd_convert_dq_blocked_kernel");
 }
 int bwd_post(const FaBwdArgs& a, cudaStream_t st) {
   return a.dtype == FA_DTYPE_BF16 ? bwd_post_t<__nv_bfloat16>(a, st) : bwd_post_t<__half>(a, st);

@@ -19,6 +19,8 @@
 // Warps: 0-7 compute (warpgroup w handles query columns [64w, 64w+64) of the block; at the drain
 // and in the epilogue, head-dim columns [D/2*w, ...)), 8 = TMA producer, 9 = MMA issuer,
 // 10 = loader of the per-row LSE / D vectors, 11 = TMEM owner.
+#include <cstdlib>
+
 #include "../fa_common.cuh"
 #include "ptx.cuh"
 #include "tma_host.cuh"
@@ -55,6 +57,8 @@ struct BCfg {
 struct BwdTcParams {
   CUtensorMap tq, tk, tv, tdo;
   FaBwdArgs a;
+  int debug;      // timing experiments only (FA_B200_DEBUG_BWD); 0 in normal use
+  int dq_blocks;  // 128-row blocks per (batch, head) [packed input: per head] of the blocked dq_accum
 };
 
 template <typename T>
@@ -114,7 +118,7 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
     mbar_init(bar_kv, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_qdo_full(s), 1);
-      mbar_init(bar_qdo_empty(s), 1);
+      mbar_init(bar_qdo_empty(s), 9);  // the MMA commit + 8 warps that staged their dQ piece in the slot
       mbar_init(bar_st_full(s), 1);
       mbar_init(bar_st_empty(s), 8);
     }
@@ -149,7 +153,7 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
     const int key = n0 + kr;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_off + C::COL_S, tdP = tmem + lane_off + C::COL_DP;
-    bool ok = run;
+    bool ok = (*abort_flag == 0);  // with iters == 0 the loop is skipped and the epilogue writes zeros
     for (int it = 0; it < iters && ok; ++it) {
       const int slot = it & 1, par = (it >> 1) & 1;
       const int m0 = mblk_of(it) * kB;
@@ -176,7 +180,8 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
       float p[64];
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
-        float x = fast_exp2(fmaf(__uint_as_float(su[c >> 5][c & 31]), scale_log2, -lse2[c]));
+        float x = (P.debug & 4) ? __uint_as_float(su[c >> 5][c & 31]) * 1e-3f
+                                : fast_exp2(fmaf(__uint_as_float(su[c >> 5][c & 31]), scale_log2, -lse2[c]));
         if (need_mask) {
           const int cc = w * 64 + c;
           x = (cc >= c_lo && cc <= c_hi) ? x : 0.f;
@@ -232,29 +237,36 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
       if (!ok) break;
       tc_fence_after();
       {
-        const int qrow = m0 + kr;
-        float* dst = a.dq_accum + (((int64_t)si.q_batch * a.seqlen_q + si.q_row0 + qrow) * a.heads + hq) * a.head_dim;
+        // TMEM -> registers; the dP^T/dQ columns are free again as soon as the loads have landed
+        uint32_t o[DH / 64][32];
 #pragma unroll
-        for (int c0 = 0; c0 < DH / 2; c0 += 32) {
-          uint32_t o[32];
-          tmem_ld32(tdP + w * (DH / 2) + c0, o);
-          tmem_wait_ld();
-          if (qrow < si.sq) {
+        for (int j = 0; j < DH / 64; ++j) tmem_ld32(tdP + w * (DH / 2) + j * 32, o[j]);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_dq_empty);
+        // registers -> shared staging (the Q / dO tile of this block, which no MMA reads any more), laid out
+        // exactly like the warp's 32-row piece of the blocked dq_accum: [4-column chunk][row][4 floats]
+        constexpr int kWarpBytes = 32 * (DH / 2) * 4;
+        unsigned char* stage = smem + C::OFF_QDO + slot * 2 * C::TILE_BYTES + w * C::TILE_BYTES + (warp & 3) * kWarpBytes;
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const int col = w * (DH / 2) + c0 + i;
-              if (col < a.head_dim)
-                red_add_v4(dst + col, __uint_as_float(o[i]), __uint_as_float(o[i + 1]), __uint_as_float(o[i + 2]),
-                           __uint_as_float(o[i + 3]));
-            }
-          }
+        for (int c4 = 0; c4 < DH / 8; ++c4)
+          *reinterpret_cast<uint4*>(stage + (c4 * 32 + lane) * 16) =
+              make_uint4(o[(4 * c4) >> 5][(4 * c4) & 31], o[(4 * c4) >> 5][(4 * c4 + 1) & 31],
+                         o[(4 * c4) >> 5][(4 * c4 + 2) & 31], o[(4 * c4) >> 5][(4 * c4 + 3) & 31]);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          const int64_t blk = dq_block_index(a.cu_seqlens_q != nullptr, b, hq, a.heads, (int)si.q_row0, P.dq_blocks) + mblk_of(it);
+          float* gdst = a.dq_accum + ((blk * 2 + w) * 4 + (warp & 3)) * (int64_t)(kWarpBytes / 4);
+          if (!(P.debug & 1)) bulk_reduce_add_f32(gdst, smem_addr(stage), kWarpBytes);
+          bulk_commit_wait_read();
+          mbar_arrive(bar_qdo_empty(slot));  // the staging bytes have been read: the slot may be refilled
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_dq_empty);
     }
 
+    if (lane == 0) bulk_wait_all();  // the dQ reductions of this warp have been performed
     // ---- epilogue: dK (scaled) and dV
     if (ok && *abort_flag == 0) {
       const uint32_t tdV = tmem + lane_off + C::COL_DV, tdK = tmem + lane_off + C::COL_DK;
@@ -393,12 +405,14 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
 #pragma unroll
           for (int kk = 0; kk < kB / 16; ++kk) {
             const uint32_t aoff = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
+            if (!(P.debug & 16))
             mma_ss(tmem + C::COL_DK, smem_desc_sw128(sDS + aoff, 16, 1024),
                    smem_desc_sw128(sQ(slot) + kk * 2048, kChunkBytes, 1024), idesc_dv, (it > 0) || kk > 0);
           }
           // dQ = dS K  (over the dP^T columns, which the compute warps have consumed)
 #pragma unroll
           for (int kk = 0; kk < kB / 16; ++kk)
+            if (!(P.debug & 8))
             mma_ss(tmem + C::COL_DP, smem_desc_sw128(sDS + kk * 2048, kChunkBytes, 1024),
                    smem_desc_sw128(sK + kk * 2048, kChunkBytes, 1024), idesc_dq, kk > 0);
           tc_commit(bar_dq_full);
@@ -438,6 +452,11 @@ int launch_bwd_tc(const FaBwdArgs& a, cudaStream_t st) {
   using C = BCfg<DH>;
   BwdTcParams P;
   P.a = a;
+  {
+    const char* dbg = getenv("FA_B200_DEBUG_BWD");
+    P.debug = dbg ? atoi(dbg) : 0;
+    P.dq_blocks = dq_blocks_per_unit(a.cu_seqlens_q != nullptr, a.seqlen_q, a.total_q, a.batch);
+  }
   const bool varlen = a.cu_seqlens_q != nullptr;
   const int64_t q_rows = varlen ? a.total_q : a.seqlen_q, k_rows = varlen ? a.total_k : a.seqlen_k;
   const int64_t nb = varlen ? 1 : a.batch;

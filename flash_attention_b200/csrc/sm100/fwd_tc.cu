@@ -17,6 +17,8 @@
 //
 // Same math as compute_attn_1rowblock (csrc/flash_attn/src/flash_fwd_kernel.h:74-580); mask rule of
 // csrc/flash_attn/src/softmax.h:142-179; O = 0 and LSE = +inf for rows without a visible key.
+#include <cstdlib>
+
 #include "../fa_common.cuh"
 #include "ptx.cuh"
 #include "tma_host.cuh"
@@ -49,6 +51,7 @@ struct Cfg {
 struct FwdTcParams {
   CUtensorMap tq, tk, tv;
   FaFwdArgs a;
+  int debug;  // timing experiments only (FA_B200_DEBUG_FWD); 0 in normal use
 };
 
 template <typename T>
@@ -189,7 +192,7 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
         mx2 = fmaxf(mx2, S_AT(c + 2));
         mx3 = fmaxf(mx3, S_AT(c + 3));
       }
-      const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+      const float m_blk = (P.debug & 2) ? 0.f : fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
       const float m_cand = fmaxf(m_used, m_blk);
       const bool grow = m_cand > m_used + kRescaleThreshold;  // also true when m_used is -inf and m_cand is finite
       if (it > 0 && __any_sync(0xffffffffu, grow)) {
@@ -215,8 +218,8 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
       float l0 = 0.f, l1 = 0.f;
 #pragma unroll
       for (int c = 0; c < 128; c += 2) {
-        float e0 = fast_exp2(fmaf(S_AT(c), scale_log2, neg_m));
-        float e1 = fast_exp2(fmaf(S_AT(c + 1), scale_log2, neg_m));
+        float e0 = (P.debug & 1) ? S_AT(c) * 1e-3f : fast_exp2(fmaf(S_AT(c), scale_log2, neg_m));
+        float e1 = (P.debug & 1) ? S_AT(c + 1) * 1e-3f : fast_exp2(fmaf(S_AT(c + 1), scale_log2, neg_m));
         l0 += e0;
         l1 += e1;
         pu[c >> 6][(c >> 1) & 31] = Pack<T>::two(e0, e1);
@@ -329,6 +332,7 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
           const uint32_t d = tmem + (t ? C::COL_S1 : C::COL_S0);
 #pragma unroll
           for (int kk = 0; kk < DH / 16; ++kk) {
+            if ((P.debug & 4) && kk > 0) break;
             const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
             const uint64_t ad = smem_desc_sw128(sQ + t * C::TILE_BYTES + off, 16, 1024);
             const uint64_t bd = smem_desc_sw128(sKV + slot * C::TILE_BYTES + off, 16, 1024);
@@ -341,6 +345,7 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
           const uint32_t pa = tmem + (t ? C::COL_S1 : C::COL_S0);
 #pragma unroll
           for (int kk = 0; kk < kBN / 16; ++kk) {
+            if ((P.debug & 8) && kk > 0) break;
             const uint64_t bd = smem_desc_sw128(sKV + slot * C::TILE_BYTES + kk * 2048, kChunkBytes, 1024);
             mma_ts(d, pa + kk * 8, bd, idesc_o, (!first) || kk > 0);
           }
@@ -410,6 +415,10 @@ int launch_fwd_tc(const FaFwdArgs& a, cudaStream_t st) {
   using C = Cfg<DH>;
   FwdTcParams P;
   P.a = a;
+  {
+    const char* dbg = getenv("FA_B200_DEBUG_FWD");
+    P.debug = dbg ? atoi(dbg) : 0;
+  }
   const bool varlen = a.cu_seqlens_q != nullptr;
   const int64_t q_rows = varlen ? a.total_q : a.seqlen_q, k_rows = varlen ? a.total_k : a.seqlen_k;
   const int64_t nb = varlen ? 1 : a.batch;

@@ -59,7 +59,7 @@ class CudaBlockOps:
         dq = torch.empty_like(q)
         d_seqlen = (Sq + 127) // 128 * 128
         softmax_d = torch.empty((B, H, d_seqlen), dtype=torch.float32, device=q.device)
-        dq_accum = torch.empty(B * Sq * H * D, dtype=torch.float32, device=q.device)
+        dq_accum = torch.empty(lib().fa_bwd_workspace_bytes(B, Sq, H, D, 0, 0) // 4, dtype=torch.float32, device=q.device)
         a = FaBwdArgs()
         a.q, a.k, a.v, a.out, a.dout, a.dq = (tensor3(x) for x in (q, k, v, out, dout, dq))
         a.softmax_lse, a.lse_seqlen = ptr(lse), lse.shape[-1]

@@ -72,14 +72,17 @@ def _sm_count(dev):
 
 
 def _windows(is_causal, wl, wr, seqlen_k):
-    # flash_api.cpp:296-297 and set_params_fprop (flash_api.cpp:105-115)
-    if wl >= seqlen_k:
-        wl = -1
-    if wr >= seqlen_k:
-        wr = -1
+    # flash_api.cpp:297 (causal means right window 0) and set_params_fprop (flash_api.cpp:113-114):
+    # a window that is open on one side only gets seqlen_k on the open side.  That is NOT the same
+    # as unbounded when seqlen_q > seqlen_k, and the reference's behaviour is kept as it is.
+    wl, wr = int(wl), int(wr)
     if is_causal:
         wr = 0
-    return int(wl), int(wr)
+    if wl < 0 and wr >= 0:
+        wl = int(seqlen_k)
+    if wl >= 0 and wr < 0:
+        wr = int(seqlen_k)
+    return wl, wr
 
 
 def _philox(gen, p_dropout, batch, heads, device):

