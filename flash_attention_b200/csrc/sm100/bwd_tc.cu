@@ -13,8 +13,11 @@
 //   dV  += P^T  dO        A = P^T from TMEM, B = dO tile (MN-major)     -> TMEM tdV
 //   dK  += dS^T Q         A = dS^T from shared (K-major), B = Q tile    -> TMEM tdK
 //   dQ   = dS   K         A = the same dS^T bytes read MN-major, B = K  -> TMEM (over tdP)
-// dQ is drained from TMEM with vector fp32 reductions into the dq_accum workspace that
-// bwd_dot_do_o_kernel zeroed; bwd_convert_dq_kernel scales and casts it (generic_bwd.cu).
+// dQ leaves TMEM through registers into the shared-memory slot of the block's (already consumed)
+// Q / dO tiles and from there, one bulk fp32 add-reduction of 8 KiB per warp, into a BLOCKED dq_accum
+// workspace (fa_common.cuh: dq_blocked_offset) that the host cleared; bwd_convert_dq_blocked_kernel
+// scales and casts it (generic_bwd.cu).  Scattered 16-byte red.global reductions were measured at
+// 37 % of the kernel's time; the bulk form adds whole lines at the memory side.
 //
 // Warps: 0-7 compute (warpgroup w handles query columns [64w, 64w+64) of the block; at the drain
 // and in the epilogue, head-dim columns [D/2*w, ...)), 8 = TMA producer, 9 = MMA issuer,
@@ -71,10 +74,6 @@ template <>
 struct BFmt<__nv_bfloat16> {
   static constexpr int kIdesc = 1;
 };
-
-__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 
 template <typename T, int DH>
 __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ BwdTcParams P) {
@@ -179,14 +178,20 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
       tmem_wait_ld();
       float p[64];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float x = (P.debug & 4) ? __uint_as_float(su[c >> 5][c & 31]) * 1e-3f
-                                : fast_exp2(fmaf(__uint_as_float(su[c >> 5][c & 31]), scale_log2, -lse2[c]));
-        if (need_mask) {
-          const int cc = w * 64 + c;
-          x = (cc >= c_lo && cc <= c_hi) ? x : 0.f;
+      for (int c4 = 0; c4 < 16; ++c4) {
+        const float4 l4 = reinterpret_cast<const float4*>(lse2)[c4];
+        const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int c = c4 * 4 + e;
+          float x = (P.debug & 4) ? __uint_as_float(su[c >> 5][c & 31]) * 1e-3f
+                                  : fast_exp2(fmaf(__uint_as_float(su[c >> 5][c & 31]), scale_log2, -lv[e]));
+          if (need_mask) {
+            const int cc = w * 64 + c;
+            x = (cc >= c_lo && cc <= c_hi) ? x : 0.f;
+          }
+          p[c] = x;
         }
-        p[c] = x;
       }
       // both warpgroups must have read S^T before P^T is written over its columns (a bounded
       // mbarrier rendezvous rather than bar.sync, so that an aborting kernel cannot strand a warp)
@@ -212,16 +217,17 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
         unsigned char* ds_row = smem + C::OFF_DS + w * kChunkBytes + kr * 128;
 #pragma unroll
         for (int c16 = 0; c16 < 8; ++c16) {
-          uint4 v;
-          uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
+          const float4 da = reinterpret_cast<const float4*>(dsum)[c16 * 2], db = reinterpret_cast<const float4*>(dsum)[c16 * 2 + 1];
+          const float dv8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+          uint32_t vv[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int c = c16 * 8 + e * 2;
-            const float d0 = p[c] * (__uint_as_float(su[c >> 5][c & 31]) - dsum[c]);
-            const float d1 = p[c + 1] * (__uint_as_float(su[(c + 1) >> 5][(c + 1) & 31]) - dsum[c + 1]);
+            const float d0 = p[c] * (__uint_as_float(su[c >> 5][c & 31]) - dv8[e * 2]);
+            const float d1 = p[c + 1] * (__uint_as_float(su[(c + 1) >> 5][(c + 1) & 31]) - dv8[e * 2 + 1]);
             vv[e] = Pack<T>::two(d0, d1);
           }
-          *reinterpret_cast<uint4*>(ds_row + (((c16 ^ kr) & 7) << 4)) = v;
+          *reinterpret_cast<uint4*>(ds_row + (((c16 ^ kr) & 7) << 4)) = make_uint4(vv[0], vv[1], vv[2], vv[3]);
         }
       }
       tmem_wait_st();

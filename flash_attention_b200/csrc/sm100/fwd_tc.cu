@@ -168,11 +168,16 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
       if (!ok) break;
       tc_fence_after();
       uint32_t su[4][32];
-      tmem_ld32(tS + 0, su[0]);
-      tmem_ld32(tS + 32, su[1]);
-      tmem_ld32(tS + 64, su[2]);
-      tmem_ld32(tS + 96, su[3]);
-      tmem_wait_ld();
+      if (P.debug & 16) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) su[c >> 5][c & 31] = 0u;
+      } else {
+        tmem_ld32(tS + 0, su[0]);
+        tmem_ld32(tS + 32, su[1]);
+        tmem_ld32(tS + 64, su[2]);
+        tmem_ld32(tS + 96, su[3]);
+        tmem_wait_ld();
+      }
 #define S_AT(c) __uint_as_float(su[(c) >> 5][(c) & 31])
       const int n0 = j * kBN;
       const bool need_mask = (n0 + kBN - 1 >= si.sk) ||
@@ -226,9 +231,11 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
       }
 #undef S_AT
       l_sum += l0 + l1;
-      tmem_st32(tS + 0, pu[0]);
-      tmem_st32(tS + 32, pu[1]);
-      tmem_wait_st();
+      if (!(P.debug & 32)) {
+        tmem_st32(tS + 0, pu[0]);
+        tmem_st32(tS + 32, pu[1]);
+        tmem_wait_st();
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pfull(t));
@@ -315,6 +322,10 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
           if (!ok) break;
           const int j = J_lo + (idx >> 1);
           const CUtensorMap* tm = (idx & 1) ? &P.tv : &P.tk;
+          if ((P.debug & 128) && idx >= C::STAGES) {
+            mbar_arrive(bar_full(slot));  // timing experiment: pretend the tile has landed
+            continue;
+          }
           mbar_expect_tx(bar_full(slot), C::TILE_BYTES);
           for (int c = 0; c < C::NCHUNK; ++c)
             tma_load_4d(sKV + slot * C::TILE_BYTES + c * kChunkBytes, tm, bar_full(slot), c * 64,
