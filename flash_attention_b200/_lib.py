@@ -91,6 +91,7 @@ class FaKvcacheArgs(C.Structure):
 EXPORTS = (
     "fa_fwd", "fa_bwd", "fa_fwd_kvcache", "fa_fwd_num_splits", "fa_kvcache_plan", "fa_bwd_workspace_bytes",
     "fa_combine", "fa_last_error", "fa_build_info", "fa_device_status", "fa_abi_struct_size",
+    "fa_fwd_kvcache_noalloc", "fa_noalloc_scratch_bytes",
 )
 
 _lib = None
@@ -112,6 +113,9 @@ def lib():
         L.fa_bwd.restype = C.c_int
         L.fa_fwd_kvcache.argtypes = [C.POINTER(FaKvcacheArgs), c_vp]
         L.fa_fwd_kvcache.restype = C.c_int
+        L.fa_fwd_kvcache_noalloc.argtypes = [C.POINTER(FaKvcacheArgs), c_vp]
+        L.fa_fwd_kvcache_noalloc.restype = C.c_int
+        L.fa_noalloc_scratch_bytes.restype = c_i64
         L.fa_fwd_num_splits.argtypes = [c_i32] * 6
         L.fa_fwd_num_splits.restype = C.c_int
         L.fa_kvcache_plan.argtypes = [C.POINTER(FaKvcacheArgs), c_i32, C.POINTER(c_i64), C.POINTER(c_i64)]

@@ -27,6 +27,8 @@ int bwd_tc_main(const FaBwdArgs& a, cudaStream_t st);
 bool decode_eligible(const FaKvcacheArgs& a);
 int decode_plan(const FaKvcacheArgs& a, int num_sms);
 int decode_run(const FaKvcacheArgs& a, int num_splits, cudaStream_t st);
+int decode_run_noalloc(const FaKvcacheArgs& a, int num_splits, cudaStream_t st);
+size_t decode_noalloc_capacity();
 int fwd_tc_status(bool clear);
 int decode_status(bool clear);
 int bwd_tc_status(bool clear);
@@ -323,6 +325,24 @@ int fa_fwd_kvcache(const FaKvcacheArgs* a, fa_stream_t stream) {
                        a->seqlen_q, a->head_dim, a->dtype, st);
   return 0;
 }
+
+int fa_fwd_kvcache_noalloc(const FaKvcacheArgs* a, fa_stream_t stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (kvcache_checks(a)) return 1;
+  if (check_tensor(a->q, "q") || check_tensor(a->kcache, "kcache") || check_tensor(a->vcache, "vcache") ||
+      check_tensor(a->out, "out"))
+    return 1;
+  FA_REQUIRE(fa::decode_eligible(*a),
+             "fa_fwd_kvcache_noalloc only covers the single-token decode shape: seqlen_q * heads / heads_k <= 16, head_dim 64 "
+             "or 128, no window, at most one new token");
+  FA_REQUIRE(a->softmax_lse != nullptr, "softmax_lse: null pointer");
+  int splits = fa::decode_plan(*a, fa_host::sm_count());
+  if (splits < 1) splits = 1;
+  if (a->seqlen_q == 0) return 0;
+  return fa::decode_run_noalloc(*a, splits, st);
+}
+
+int64_t fa_noalloc_scratch_bytes(void) { return (int64_t)fa::decode_noalloc_capacity(); }
 
 int fa_combine(const float* out_parts, const float* lse_parts, void* out, float* lse, int32_t n_parts, int64_t rows,
                int32_t head_dim, int64_t out_row_stride, int32_t dtype, fa_stream_t stream) {

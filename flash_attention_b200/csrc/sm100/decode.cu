@@ -489,6 +489,61 @@ int decode_run(const FaKvcacheArgs& a, int num_splits, cudaStream_t st) {
   return 0;
 }
 
+// ---- split-KV decode without any allocation by caller or library -------------------------------
+// Scratch for the per-split partial results lives in this translation unit's device image: every
+// GPU that loads the library reserves kNoAllocScratchBytes until the process exits.
+constexpr size_t kNoAllocScratchBytes = 24u << 20;  // 24 MiB
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+size_t decode_noalloc_capacity() { return kNoAllocScratchBytes; }
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address; the
+// address on the current device is looked up once per device and cached.
+static int noalloc_scratch_ptr(unsigned char** out) {
+  static unsigned char* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    fa_host::set_error("fa_fwd_kvcache_noalloc: cannot identify the current device");
+    cudaGetLastError();
+    return 2;
+  }
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      fa_host::set_error("fa_fwd_kvcache_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      cudaGetLastError();
+      return 2;
+    }
+    ptrs[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = ptrs[dev];
+  return 0;
+}
+
+int decode_run_noalloc(const FaKvcacheArgs& a, int num_splits, cudaStream_t st) {
+  const size_t rows = (size_t)a.batch * a.heads * a.seqlen_q;
+  const size_t lse_bytes = (rows * num_splits * sizeof(float) + 255) & ~size_t(255);
+  const size_t out_bytes = rows * num_splits * (size_t)a.head_dim * sizeof(float);
+  FaKvcacheArgs b = a;
+  if (num_splits > 1) {
+    if (lse_bytes + out_bytes > kNoAllocScratchBytes) {
+      fa_host::set_error(
+          "fa_fwd_kvcache_noalloc: %d splits of %zu rows need %zu bytes of scratch, the built-in buffer holds %zu; "
+          "pass a smaller num_splits or use fa_fwd_kvcache with caller-provided workspaces",
+          num_splits, rows, lse_bytes + out_bytes, (size_t)kNoAllocScratchBytes);
+      return 1;
+    }
+    unsigned char* base = nullptr;
+    if (noalloc_scratch_ptr(&base)) return 2;
+    // Nothing has to be cleared: every (split, row) LSE is written by each launch (-inf for an empty
+    // split) and the combine step never reads the partial output of a part whose weight is zero.
+    b.lse_accum = reinterpret_cast<float*>(base);
+    b.out_accum = reinterpret_cast<float*>(base + lse_bytes);
+  }
+  return decode_run(b, num_splits, st);
+}
+
 int decode_status(bool clear) {
   int v = 0;
   if (cudaDeviceSynchronize() != cudaSuccess) return -1;

@@ -142,6 +142,30 @@ int fa_bwd(const FaBwdArgs* args, fa_stream_t stream);
 /* flash_attn_2_cuda.fwd_kvcache */
 int fa_fwd_kvcache(const FaKvcacheArgs* args, fa_stream_t stream);
 
+/* Split-KV decode for callers that cannot allocate device memory.  (No counterpart in the
+   reference, whose mha_fwd_kvcache always allocates its split workspaces through torch.)
+   Some hosts of this library must not call cudaMalloc at all at decode time: an inference server
+   whose memory pool owns the whole device, a real-time loop that may not block on the allocator, a
+   plugin running inside someone else's pre-sized arena.  fa_fwd_kvcache needs lse_accum / out_accum
+   workspaces from such a caller; this variant does not.  The per-split partial results go to a
+   fixed buffer that is part of the library's device image (fa_noalloc_scratch_bytes() bytes, 24 MiB,
+   reserved on every GPU that loads the library until the process exits).  The caller still passes
+   q, the caches, the optional new token / rotary tables and out / softmax_lse; lse_accum, out_accum
+   and q_rotated in the argument struct are ignored.
+   Limits and rules:
+     - only the single-token decode shape (seqlen_q * heads / heads_k <= 16, head_dim 64 or 128, no
+       window, at most one new token); anything else is refused with status 1;
+     - num_splits * batch * heads * seqlen_q * (head_dim + 1) * 4 bytes must fit the buffer, else the
+       call is refused with a message saying so (pass a smaller num_splits);
+     - the first call on each device looks up the buffer's address (with that device current); make
+       that first call outside any stream capture;
+     - all calls share the one buffer, which keeps whatever the previous call left in it.  Nothing in
+       it needs clearing between calls (every launch rewrites every value it later reads), but two
+       calls whose kernels overlap on the GPU (different streams) race on it: serialise them;
+     - the call itself performs no cudaMalloc / cudaFree or other allocating call. */
+int fa_fwd_kvcache_noalloc(const FaKvcacheArgs* args, fa_stream_t stream);
+int64_t fa_noalloc_scratch_bytes(void);
+
 /* Number of KV splits fa_fwd would like for these sizes (num_splits_heuristic, flash_api.cpp:206-246).
    The caller sizes lse_accum/out_accum from it and passes it back in FaFwdArgs.num_splits. */
 int fa_fwd_num_splits(int32_t batch, int32_t heads, int32_t seqlen_q, int32_t seqlen_k, int32_t head_dim,

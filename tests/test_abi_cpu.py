@@ -75,6 +75,7 @@ def test_split_heuristic_matches_reference_rules(lib):
     assert lib.fa_bwd_workspace_bytes(2, 100, 4, 64, 0, 0) == max(2 * 100 * 4 * 64 * 4, 2 * 4 * 1 * 128 * 64 * 4)
     assert lib.fa_bwd_workspace_bytes(2, 100, 4, 64, 150, 1) == max(150 * 4 * 64 * 4, 4 * (150 // 128 + 2 + 1) * 128 * 64 * 4)
     assert lib.fa_bwd_workspace_bytes(16, 2048, 16, 128, 0, 0) == 16 * 2048 * 16 * 128 * 4
+    assert lib.fa_noalloc_scratch_bytes() == 24 << 20
 
 
 def test_dropin_module_has_the_reference_entry_points():
