@@ -168,16 +168,11 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
       if (!ok) break;
       tc_fence_after();
       uint32_t su[4][32];
-      if (P.debug & 16) {
-#pragma unroll
-        for (int c = 0; c < 128; ++c) su[c >> 5][c & 31] = 0u;
-      } else {
-        tmem_ld32(tS + 0, su[0]);
-        tmem_ld32(tS + 32, su[1]);
-        tmem_ld32(tS + 64, su[2]);
-        tmem_ld32(tS + 96, su[3]);
-        tmem_wait_ld();
-      }
+      tmem_ld32(tS + 0, su[0]);
+      tmem_ld32(tS + 32, su[1]);
+      tmem_ld32(tS + 64, su[2]);
+      tmem_ld32(tS + 96, su[3]);
+      tmem_wait_ld();
 #define S_AT(c) __uint_as_float(su[(c) >> 5][(c) & 31])
       const int n0 = j * kBN;
       const bool need_mask = (n0 + kBN - 1 >= si.sk) ||
@@ -197,7 +192,7 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
         mx2 = fmaxf(mx2, S_AT(c + 2));
         mx3 = fmaxf(mx3, S_AT(c + 3));
       }
-      const float m_blk = (P.debug & 2) ? 0.f : fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
+      const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2;
       const float m_cand = fmaxf(m_used, m_blk);
       const bool grow = m_cand > m_used + kRescaleThreshold;  // also true when m_used is -inf and m_cand is finite
       if (it > 0 && __any_sync(0xffffffffu, grow)) {
@@ -223,19 +218,17 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
       float l0 = 0.f, l1 = 0.f;
 #pragma unroll
       for (int c = 0; c < 128; c += 2) {
-        float e0 = (P.debug & 1) ? S_AT(c) * 1e-3f : fast_exp2(fmaf(S_AT(c), scale_log2, neg_m));
-        float e1 = (P.debug & 1) ? S_AT(c + 1) * 1e-3f : fast_exp2(fmaf(S_AT(c + 1), scale_log2, neg_m));
+        float e0 = fast_exp2(fmaf(S_AT(c), scale_log2, neg_m));
+        float e1 = fast_exp2(fmaf(S_AT(c + 1), scale_log2, neg_m));
         l0 += e0;
         l1 += e1;
         pu[c >> 6][(c >> 1) & 31] = Pack<T>::two(e0, e1);
       }
 #undef S_AT
       l_sum += l0 + l1;
-      if (!(P.debug & 32)) {
-        tmem_st32(tS + 0, pu[0]);
-        tmem_st32(tS + 32, pu[1]);
-        tmem_wait_st();
-      }
+      tmem_st32(tS + 0, pu[0]);
+      tmem_st32(tS + 32, pu[1]);
+      tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pfull(t));
@@ -322,10 +315,6 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
           if (!ok) break;
           const int j = J_lo + (idx >> 1);
           const CUtensorMap* tm = (idx & 1) ? &P.tv : &P.tk;
-          if ((P.debug & 128) && idx >= C::STAGES) {
-            mbar_arrive(bar_full(slot));  // timing experiment: pretend the tile has landed
-            continue;
-          }
           mbar_expect_tx(bar_full(slot), C::TILE_BYTES);
           for (int c = 0; c < C::NCHUNK; ++c)
             tma_load_4d(sKV + slot * C::TILE_BYTES + c * kChunkBytes, tm, bar_full(slot), c * 64,
@@ -343,7 +332,6 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
           const uint32_t d = tmem + (t ? C::COL_S1 : C::COL_S0);
 #pragma unroll
           for (int kk = 0; kk < DH / 16; ++kk) {
-            if ((P.debug & 4) && kk > 0) break;
             const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
             const uint64_t ad = smem_desc_sw128(sQ + t * C::TILE_BYTES + off, 16, 1024);
             const uint64_t bd = smem_desc_sw128(sKV + slot * C::TILE_BYTES + off, 16, 1024);
@@ -356,7 +344,6 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
           const uint32_t pa = tmem + (t ? C::COL_S1 : C::COL_S0);
 #pragma unroll
           for (int kk = 0; kk < kBN / 16; ++kk) {
-            if ((P.debug & 8) && kk > 0) break;
             const uint64_t bd = smem_desc_sw128(sKV + slot * C::TILE_BYTES + kk * 2048, kChunkBytes, 1024);
             mma_ts(d, pa + kk * 8, bd, idesc_o, (!first) || kk > 0);
           }

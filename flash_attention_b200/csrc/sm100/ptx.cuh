@@ -42,12 +42,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait that lets the hardware park the thread for up to `ns` nanoseconds while the phase is
+// incomplete (it is woken when the phase completes), instead of returning at once to a spin loop
+// that competes for issue slots with the warps doing useful work on the same scheduler.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Returns false (and records `code`) when the wait gave up or the kernel is already aborting.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code, volatile int* abort_flag,
+                                          int mode = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t polls = 0;
   while (true) {
+    if (mode == 1) {
+      if (mbar_try_wait_parked(bar, parity, 2000)) return true;
+    } else if (mode == 2) {
+      __nanosleep(40);
+    }
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 63u) == 0) {
       if (*abort_flag) return false;
@@ -64,7 +84,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
-// 4-D tiled load, no multicast.  c0 is the innermost (contiguous) coordinate and must keep
+// 4-D tiled load into this CTA's own shared memory only.  c0 is the innermost (contiguous) coordinate and must keep
 // c0 * sizeof(element) a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2,
                                             int c3) {
@@ -191,6 +211,41 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int ab_format, i
          | ((uint32_t)b_mn_major << 16)      // B major
          | ((uint32_t)(N >> 3) << 17)        // N / 8
          | ((uint32_t)(M >> 4) << 24);       // M / 16
+}
+
+// ---- packed fp32 pairs (sm_100 has two-wide fp32 FMA/ADD and a three-input max) ------------------
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
