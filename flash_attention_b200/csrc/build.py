@@ -22,6 +22,7 @@ SOURCES = [
     "kvcache_prep.cu",
     "sm100/fwd_tc.cu",
     "sm100/bwd_tc.cu",
+    "sm100/bwd_dq_tc.cu",
     "sm100/decode.cu",
 ]
 

@@ -32,6 +32,8 @@ size_t decode_noalloc_capacity();
 int fwd_tc_status(bool clear);
 int decode_status(bool clear);
 int bwd_tc_status(bool clear);
+int bwd_dq_tc_main(const FaBwdArgs& a, cudaStream_t st);
+int bwd_dq_tc_status(bool clear);
 }  // namespace fa
 
 namespace fa_host {
@@ -93,7 +95,7 @@ extern "C" {
 const char* fa_last_error(void) { return fa_host::g_err; }
 
 const char* fa_build_info(void) {
-  return "libfa_b200 arch=sm_100a kernels=fwd_tc(tcgen05+TMA),bwd_tc(tcgen05+TMA),decode_splitkv(TMA),"
+  return "libfa_b200 arch=sm_100a kernels=fwd_tc(tcgen05+TMA),bwd_dkdv_tc(tcgen05+TMA),bwd_dq_tc(tcgen05+TMA),decode_splitkv(TMA),"
          "fwd_generic(mma.sync),bwd_generic(mma.sync),combine,bwd_dot_do_o,bwd_convert_dq,kvcache_prep";
 }
 
@@ -101,7 +103,8 @@ int fa_device_status(void) {
   int s = fa::fwd_tc_status(true);
   int d = fa::decode_status(true);
   int w = fa::bwd_tc_status(true);
-  return s ? s : (w ? w : d);
+  int q = fa::bwd_dq_tc_status(true);
+  return s ? s : (w ? w : (q ? q : d));
 }
 
 int fa_abi_struct_size(int32_t which) {
@@ -206,23 +209,13 @@ int fa_bwd(const FaBwdArgs* a, fa_stream_t stream) {
   FA_REQUIRE(a->d_seqlen >= a->seqlen_q, "softmax_d row pitch is smaller than seqlen_q");
   if (a->seqlen_q == 0 || a->batch == 0) return 0;
   const bool tc = a->seqlen_k > 0 && !fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::bwd_tc_eligible(*a);
-  const int dhp = a->head_dim <= 64 ? 64 : 128;
-  if (tc) {
-    // the tensor-core kernel adds whole 128-row blocks into a blocked accumulator: clear all of it
-    const bool varlen = a->cu_seqlens_q != nullptr;
-    const int64_t units = varlen ? (int64_t)a->heads : (int64_t)a->batch * a->heads;
-    const int64_t bytes = units * fa::dq_blocks_per_unit(varlen, a->seqlen_q, a->total_q, a->batch) * 128 * dhp * (int64_t)sizeof(float);
-    if (cudaMemsetAsync(a->dq_accum, 0, (size_t)bytes, st) != cudaSuccess) {
-      fa_host::set_error("clearing dq_accum failed: %s", cudaGetErrorString(cudaGetLastError()));
-      return 2;
-    }
-  }
+  // the tensor-core path writes dq directly (two kernels: dK / dV per key block, dQ per query block)
   int rc = fa::bwd_pre(*a, tc ? 0 : 1, st);
   if (rc) return rc;
   if (tc) {
     rc = fa::bwd_tc_main(*a, st);
     if (rc) return rc;
-    return fa::bwd_post_blocked(*a, dhp, st);
+    return fa::bwd_dq_tc_main(*a, st);
   }
   if (a->seqlen_k > 0) {
     rc = fa::bwd_generic_main(*a, st);

@@ -1,27 +1,29 @@
-// Backward attention main loop on tcgen05 tensor cores (head dim <= 128).
+// Backward attention on tcgen05 tensor cores (head dim <= 128), part 1 of 2: dK and dV.
+//
+// The backward pass is split in two kernels that each keep their result stationary in tensor memory
+// and recompute S and dP: this one (dK, dV; one CTA per 128 keys) and bwd_dq_tc.cu (dQ; one CTA per
+// 128 queries).  The single-kernel form of the reference, compute_dq_dk_dv_1colblock
+// (csrc/flash_attn/src/flash_bwd_kernel.h:425-1112), adds every block's dQ into an fp32 accumulator
+// with atomics; on this GPU an SM sustains only ~26 bytes/clk of fp32 reductions into the L2 (64 KiB
+// per block = ~2500 cycles, about the block's whole tensor-core time), and the saturated L2 triples
+// the latency of the Q / dO tile loads.  Two more MMAs per block cost less than that, need no
+// workspace, and make the gradient deterministic.
 //
 // One CTA owns 128 keys of one (batch, KV head) and walks every 128-row query block that can see
 // them, for every query head of the KV head's group (so grouped-query dK/dV need no expanded
-// temporaries or group reduction, cf. flash_api.cpp:744-751, 799-803, and stay free of atomics).
-// Same math as compute_dq_dk_dv_1colblock (csrc/flash_attn/src/flash_bwd_kernel.h:425-1112), but
-// everything is computed TRANSPOSED so that the operands the tensor cores need next are already
-// where tcgen05 wants them:
+// temporaries or group reduction, cf. flash_api.cpp:744-751, 799-803).  Everything is computed
+// TRANSPOSED so that the operands the tensor cores need next are already where tcgen05 wants them:
 //   S^T  = K Q^T          (lanes = keys, columns = queries)            SS MMA  -> TMEM tS
 //   dP^T = V dO^T                                                       SS MMA  -> TMEM tdP
-//   P^T  = exp2(S^T*scale*log2e - LSE*log2e)        one thread per key  -> TMEM (16-bit, over tS)
-//   dS^T = P^T o (dP^T - D)                                             -> shared, [key][query]
+//   P^T  = exp2(S^T*scale*log2e - LSE*log2e)        one thread per key  -> TMEM (16-bit, over tdP)
+//   dS^T = P^T o (dP^T - D)                                             -> TMEM (16-bit, over tdP)
 //   dV  += P^T  dO        A = P^T from TMEM, B = dO tile (MN-major)     -> TMEM tdV
-//   dK  += dS^T Q         A = dS^T from shared (K-major), B = Q tile    -> TMEM tdK
-//   dQ   = dS   K         A = the same dS^T bytes read MN-major, B = K  -> TMEM (over tdP)
-// dQ leaves TMEM through registers into the shared-memory slot of the block's (already consumed)
-// Q / dO tiles and from there, one bulk fp32 add-reduction of 8 KiB per warp, into a BLOCKED dq_accum
-// workspace (fa_common.cuh: dq_blocked_offset) that the host cleared; bwd_convert_dq_blocked_kernel
-// scales and casts it (generic_bwd.cu).  Scattered 16-byte red.global reductions were measured at
-// 37 % of the kernel's time; the bulk form adds whole lines at the memory side.
+//   dK  += dS^T Q         A = dS^T from TMEM, B = Q tile (MN-major)      -> TMEM tdK
 //
-// Warps: 0-7 compute (warpgroup w handles query columns [64w, 64w+64) of the block; at the drain
-// and in the epilogue, head-dim columns [D/2*w, ...)), 8 = TMA producer, 9 = MMA issuer,
-// 10 = loader of the per-row LSE / D vectors, 11 = TMEM owner.
+// Warps: 0-7 compute (warpgroup w handles query columns [64w, 64w+64) of the block; in the
+// epilogue, head-dim columns [D/2*w, ...)), 8 = TMA producer, 9 = MMA issuer, 10 = loader of the
+// per-row LSE / D vectors and TMEM owner, 11 idle (setmaxnreg is a warpgroup-wide instruction).
+// #define FA_BWD_TIMERS 1  // per-phase cycle counters, read through fa_bwd_timers / fa_bwd_dq_timers
 #include <cstdlib>
 
 #include "../fa_common.cuh"
@@ -37,21 +39,26 @@ namespace {
 constexpr int kB = 128;                 // query rows per block == keys per CTA
 constexpr int kChunkBytes = 128 * 128;  // [128 rows][64 x 16-bit]
 
+constexpr int kThreads = 384;
+constexpr int kWarpProducer = 8, kWarpMma = 9, kWarpStats = 10;
+constexpr int kRegsCompute = 200, kRegsOther = 72;
+
 enum BwdWait { W_B_KV = 21, W_B_QDO_FULL = 22, W_B_QDO_EMPTY = 23, W_B_STATS_FULL = 24, W_B_STATS_EMPTY = 25,
-               W_B_S = 26, W_B_DP = 27, W_B_PDS = 28, W_B_DQ_FULL = 29, W_B_DQ_EMPTY = 30, W_B_ALIGN = 20 };
+               W_B_S = 26, W_B_DP = 27, W_B_PDS = 28, W_B_ALIGN = 20 };
 
 template <int DH>
 struct BCfg {
   static constexpr int NCHUNK = DH / 64;
   static constexpr int TILE_BYTES = NCHUNK * kChunkBytes;  // one Q / dO / K / V tile
-  static constexpr int DS_BYTES = 2 * kChunkBytes;         // dS^T: 128 keys x 128 queries x 16-bit
+  // Q(i) is needed from S^T(i) (issued a block early) to dK(i), dO(i) from dP^T(i) to dV(i): Q gets the deeper ring
+  static constexpr int NSQ = 3, NSO = 2;
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = TILE_BYTES;
-  static constexpr int OFF_QDO = 2 * TILE_BYTES;           // 2 slots x (Q, dO)
-  static constexpr int OFF_DS = OFF_QDO + 4 * TILE_BYTES;
-  static constexpr int OFF_STATS = OFF_DS + DS_BYTES;      // 2 slots x (128 lse2, 128 dsum) fp32
+  static constexpr int OFF_Q = 2 * TILE_BYTES;
+  static constexpr int OFF_DO = OFF_Q + NSQ * TILE_BYTES;
+  static constexpr int OFF_STATS = OFF_DO + NSO * TILE_BYTES;  // 2 slots x (128 lse2, 128 dsum) fp32
   static constexpr int OFF_BAR = OFF_STATS + 2 * 1024;
-  static constexpr int NBAR = 16;
+  static constexpr int NBAR = 24;
   static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16;
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + DH;
   static constexpr int TMEM_COLS = 512;
@@ -60,8 +67,6 @@ struct BCfg {
 struct BwdTcParams {
   CUtensorMap tq, tk, tv, tdo;
   FaBwdArgs a;
-  int debug;      // timing experiments only (FA_B200_DEBUG_BWD); 0 in normal use
-  int dq_blocks;  // 128-row blocks per (batch, head) [packed input: per head] of the blocked dq_accum
 };
 
 template <typename T>
@@ -75,24 +80,34 @@ struct BFmt<__nv_bfloat16> {
   static constexpr int kIdesc = 1;
 };
 
+#ifdef FA_BWD_TIMERS
+__device__ unsigned long long g_bwd_t[32];
+#define TMR(i) do { long long t_ = clock64(); tm[i] += t_ - tprev; tprev = t_; } while (0)
+#else
+#define TMR(i) do {} while (0)
+#endif
+
 template <typename T, int DH>
-__global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ BwdTcParams P) {
+__global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_constant__ BwdTcParams P) {
   using C = BCfg<DH>;
   const FaBwdArgs& a = P.a;
   extern __shared__ __align__(1024) unsigned char smem[];
   const uint32_t s_base = smem_addr(smem);
-  const uint32_t sK = s_base + C::OFF_K, sV = s_base + C::OFF_V, sDS = s_base + C::OFF_DS;
-  auto sQ = [&](int slot) { return s_base + C::OFF_QDO + slot * 2 * C::TILE_BYTES; };
-  auto sDO = [&](int slot) { return s_base + C::OFF_QDO + slot * 2 * C::TILE_BYTES + C::TILE_BYTES; };
+  constexpr int NSQ = C::NSQ, NSO = C::NSO;
+  const uint32_t sK = s_base + C::OFF_K, sV = s_base + C::OFF_V;
+  auto sQ = [&](int slot) { return s_base + C::OFF_Q + slot * C::TILE_BYTES; };
+  auto sDO = [&](int slot) { return s_base + C::OFF_DO + slot * C::TILE_BYTES; };
   float* sStats = reinterpret_cast<float*>(smem + C::OFF_STATS);
   const uint32_t bar0 = s_base + C::OFF_BAR;
   const uint32_t bar_kv = bar0;
-  auto bar_qdo_full = [&](int s) { return bar0 + 8 * (1 + s); };
-  auto bar_qdo_empty = [&](int s) { return bar0 + 8 * (3 + s); };
-  auto bar_st_full = [&](int s) { return bar0 + 8 * (5 + s); };
-  auto bar_st_empty = [&](int s) { return bar0 + 8 * (7 + s); };
-  const uint32_t bar_s = bar0 + 8 * 9, bar_dp = bar0 + 8 * 10, bar_pds = bar0 + 8 * 11, bar_dq_full = bar0 + 8 * 12,
-                 bar_dq_empty = bar0 + 8 * 13, bar_sread = bar0 + 8 * 14;
+  auto bar_q_full = [&](int s) { return bar0 + 8 * (1 + s); };
+  auto bar_q_empty = [&](int s) { return bar0 + 8 * (4 + s); };
+  auto bar_do_full = [&](int s) { return bar0 + 8 * (7 + s); };
+  auto bar_do_empty = [&](int s) { return bar0 + 8 * (9 + s); };
+  auto bar_st_full = [&](int s) { return bar0 + 8 * (11 + s); };
+  auto bar_st_empty = [&](int s) { return bar0 + 8 * (13 + s); };
+  const uint32_t bar_s = bar0 + 8 * 15, bar_dp = bar0 + 8 * 16, bar_ds = bar0 + 8 * 17, bar_p = bar0 + 8 * 18,
+                 bar_sread = bar0 + 8 * 19;
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_BAR + C::NBAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_BAR + C::NBAR * 8 + 4);
 
@@ -115,22 +130,25 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
       atomicCAS(&g_status, 0, (int)W_B_ALIGN);
     }
     mbar_init(bar_kv, 1);
+    for (int s = 0; s < NSQ; ++s) {
+      mbar_init(bar_q_full(s), 1);
+      mbar_init(bar_q_empty(s), 1);
+    }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(bar_qdo_full(s), 1);
-      mbar_init(bar_qdo_empty(s), 9);  // the MMA commit + 8 warps that staged their dQ piece in the slot
+      mbar_init(bar_do_full(s), 1);
+      mbar_init(bar_do_empty(s), 1);
       mbar_init(bar_st_full(s), 1);
       mbar_init(bar_st_empty(s), 8);
     }
     mbar_init(bar_s, 1);
     mbar_init(bar_dp, 1);
-    mbar_init(bar_pds, 8);
-    mbar_init(bar_dq_full, 1);
-    mbar_init(bar_dq_empty, 8);
+    mbar_init(bar_ds, 8);
+    mbar_init(bar_p, 8);
     mbar_init(bar_sread, 8);
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 11) {
+  if (warp == kWarpStats) {
     tmem_alloc(smem_addr(const_cast<uint32_t*>(tmem_ptr_smem)), C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -141,22 +159,34 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
   const bool run = (*abort_flag == 0) && iters > 0;
 
   const float scale_log2 = a.softmax_scale * kLog2e;
-  auto head_of = [&](int it) { return hk * group + it / nmb; };
-  auto mblk_of = [&](int it) { return m_lo + it % nmb; };
+  // (query head, query block) of iteration `it`, stepped without divisions: blocks m_lo..m_hi-1 of one head, then the next head
+  struct Walk {
+    int mb, hq, lo, hi;
+    __device__ void next() {
+      if (++mb == hi) {
+        mb = lo;
+        ++hq;
+      }
+    }
+  };
+  const Walk walk0{m_lo, hk * group, m_lo, m_hi};
 
   if (warp < 8) {
     // ---------------------------------------------------------------- compute warpgroups
-    setmaxnreg_inc<200>();
+    setmaxnreg_inc<kRegsCompute>();
     const int w = warp >> 2;                       // query-column half / head-dim half
     const int kr = (warp & 3) * 32 + lane;         // key row of this thread within the CTA tile
     const int key = n0 + kr;
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_off + C::COL_S, tdP = tmem + lane_off + C::COL_DP;
     bool ok = (*abort_flag == 0);  // with iters == 0 the loop is skipped and the epilogue writes zeros
-    for (int it = 0; it < iters && ok; ++it) {
+#ifdef FA_BWD_TIMERS
+    long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
+#endif
+    Walk wk = walk0;
+    for (int it = 0; it < iters && ok; ++it, wk.next()) {
       const int slot = it & 1, par = (it >> 1) & 1;
-      const int m0 = mblk_of(it) * kB;
-      const int hq = head_of(it);
+      const int m0 = wk.mb * kB;
       // per-thread visible query columns [c_lo, c_hi] of this block (c = query row - m0)
       int c_lo = 0, c_hi = min(kB, si.sq - m0) - 1;
       if (a.window_right >= 0) c_lo = max(c_lo, key - si.shift - a.window_right - m0);
@@ -165,114 +195,102 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
       const bool need_mask = (n0 + kB > si.sk) || (m0 + kB > si.sq) ||
                              (a.window_right >= 0 && n0 + kB - 1 > m0 + si.shift + a.window_right) ||
                              (a.window_left >= 0 && n0 < m0 + kB - 1 + si.shift - a.window_left);
-      ok = mbar_wait(bar_st_full(slot), par, W_B_STATS_FULL, abort_flag);
-      if (!ok) break;
-      const float* lse2 = sStats + slot * 256 + w * 64;
-      const float* dsum = sStats + slot * 256 + 128 + w * 64;
+      // ---- P^T = exp2(S^T * scale - LSE), 64 query columns per thread, into TMEM as the A operand of dV
+      TMR(5);
       ok = mbar_wait(bar_s, it & 1, W_B_S, abort_flag);
       if (!ok) break;
+      TMR(1);
+      const float* lse2 = sStats + slot * 256 + w * 64;
+      const float* dsum = sStats + slot * 256 + 128 + w * 64;
+      ok = mbar_wait(bar_st_full(slot), par, W_B_STATS_FULL, abort_flag);
+      if (!ok) break;
+      TMR(0);
       tc_fence_after();
-      uint32_t su[2][32];
-      tmem_ld32(tS + w * 64, su[0]);
-      tmem_ld32(tS + w * 64 + 32, su[1]);
-      tmem_wait_ld();
       float p[64];
+      {
+        uint32_t s0[32], s1[32];
+        tmem_ld32(tS + w * 64, s0);
+        tmem_ld32(tS + w * 64 + 32, s1);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sread);  // S^T(it) is in registers: the next S^T may overwrite it
 #pragma unroll
-      for (int c4 = 0; c4 < 16; ++c4) {
-        const float4 l4 = reinterpret_cast<const float4*>(lse2)[c4];
-        const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 l4 = reinterpret_cast<const float4*>(lse2)[c4];
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int c = c4 * 4 + e;
-          float x = (P.debug & 4) ? __uint_as_float(su[c >> 5][c & 31]) * 1e-3f
-                                  : fast_exp2(fmaf(__uint_as_float(su[c >> 5][c & 31]), scale_log2, -lv[e]));
-          if (need_mask) {
-            const int cc = w * 64 + c;
-            x = (cc >= c_lo && cc <= c_hi) ? x : 0.f;
+          for (int e = 0; e < 4; ++e) {
+            const int c = c4 * 4 + e;
+            p[c] = ex2(fmaf(__uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]), scale_log2, -lv[e]));
           }
-          p[c] = x;
         }
       }
-      // both warpgroups must have read S^T before P^T is written over its columns (a bounded
-      // mbarrier rendezvous rather than bar.sync, so that an aborting kernel cannot strand a warp)
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_sread);
-      ok = mbar_wait(bar_sread, it & 1, W_B_S, abort_flag);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int cc = w * 64 + c;
+          p[c] = (cc >= c_lo && cc <= c_hi) ? p[c] : 0.f;
+        }
+      }
+      TMR(2);
+      // ---- dP^T(it) into registers, then P^T (16-bit) over the first half of this warpgroup's dP^T
+      //      columns, where it is the A operand of dV
+      ok = mbar_wait(bar_dp, it & 1, W_B_DP, abort_flag);
       if (!ok) break;
+      TMR(3);
       tc_fence_after();
+      uint32_t d0[32], d1[32];
+      tmem_ld32(tdP + w * 64, d0);
+      tmem_ld32(tdP + w * 64 + 32, d1);
+      tmem_wait_ld();
       {
         uint32_t pk[32];
 #pragma unroll
         for (int c = 0; c < 64; c += 2) pk[c >> 1] = Pack<T>::two(p[c], p[c + 1]);
-        tmem_st32(tS + w * 32, pk);
-      }
-      ok = mbar_wait(bar_dp, it & 1, W_B_DP, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      tmem_ld32(tdP + w * 64, su[0]);
-      tmem_ld32(tdP + w * 64 + 32, su[1]);
-      tmem_wait_ld();
-      {
-        unsigned char* ds_row = smem + C::OFF_DS + w * kChunkBytes + kr * 128;
-#pragma unroll
-        for (int c16 = 0; c16 < 8; ++c16) {
-          const float4 da = reinterpret_cast<const float4*>(dsum)[c16 * 2], db = reinterpret_cast<const float4*>(dsum)[c16 * 2 + 1];
-          const float dv8[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
-          uint32_t vv[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int c = c16 * 8 + e * 2;
-            const float d0 = p[c] * (__uint_as_float(su[c >> 5][c & 31]) - dv8[e * 2]);
-            const float d1 = p[c + 1] * (__uint_as_float(su[(c + 1) >> 5][(c + 1) & 31]) - dv8[e * 2 + 1]);
-            vv[e] = Pack<T>::two(d0, d1);
-          }
-          *reinterpret_cast<uint4*>(ds_row + (((c16 ^ kr) & 7) << 4)) = make_uint4(vv[0], vv[1], vv[2], vv[3]);
-        }
+        tmem_st32(tdP + w * 64, pk);
       }
       tmem_wait_st();
       tc_fence_before();
-      fence_proxy_async();  // dS^T was written with ordinary stores and is read by the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
+      // ---- dS^T = P^T o (dP^T - D), 16-bit, over the second half of this warpgroup's dP^T columns,
+      //      where it is the A operand of dK
+      {
+        uint32_t dk[32];
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 d4 = reinterpret_cast<const float4*>(dsum)[c4];
+          const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+          for (int e = 0; e < 4; e += 2) {
+            const int c = c4 * 4 + e;
+            const float x0 = p[c] * (__uint_as_float(c < 32 ? d0[c & 31] : d1[c & 31]) - dv[e]);
+            const float x1 = p[c + 1] * (__uint_as_float(c < 32 ? d0[(c + 1) & 31] : d1[(c + 1) & 31]) - dv[e + 1]);
+            dk[c >> 1] = Pack<T>::two(x0, x1);
+          }
+        }
+        tmem_st32(tdP + w * 64 + 32, dk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(bar_st_empty(slot));
-        mbar_arrive(bar_pds);
+        mbar_arrive(bar_ds);
       }
-      // ---- drain dQ of this block: lanes are query rows now, this warpgroup takes DH/2 columns
-      ok = mbar_wait(bar_dq_full, it & 1, W_B_DQ_FULL, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      {
-        // TMEM -> registers; the dP^T/dQ columns are free again as soon as the loads have landed
-        uint32_t o[DH / 64][32];
-#pragma unroll
-        for (int j = 0; j < DH / 64; ++j) tmem_ld32(tdP + w * (DH / 2) + j * 32, o[j]);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_dq_empty);
-        // registers -> shared staging (the Q / dO tile of this block, which no MMA reads any more), laid out
-        // exactly like the warp's 32-row piece of the blocked dq_accum: [4-column chunk][row][4 floats]
-        constexpr int kWarpBytes = 32 * (DH / 2) * 4;
-        unsigned char* stage = smem + C::OFF_QDO + slot * 2 * C::TILE_BYTES + w * C::TILE_BYTES + (warp & 3) * kWarpBytes;
-#pragma unroll
-        for (int c4 = 0; c4 < DH / 8; ++c4)
-          *reinterpret_cast<uint4*>(stage + (c4 * 32 + lane) * 16) =
-              make_uint4(o[(4 * c4) >> 5][(4 * c4) & 31], o[(4 * c4) >> 5][(4 * c4 + 1) & 31],
-                         o[(4 * c4) >> 5][(4 * c4 + 2) & 31], o[(4 * c4) >> 5][(4 * c4 + 3) & 31]);
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          const int64_t blk = dq_block_index(a.cu_seqlens_q != nullptr, b, hq, a.heads, (int)si.q_row0, P.dq_blocks) + mblk_of(it);
-          float* gdst = a.dq_accum + ((blk * 2 + w) * 4 + (warp & 3)) * (int64_t)(kWarpBytes / 4);
-          if (!(P.debug & 1)) bulk_reduce_add_f32(gdst, smem_addr(stage), kWarpBytes);
-          bulk_commit_wait_read();
-          mbar_arrive(bar_qdo_empty(slot));  // the staging bytes have been read: the slot may be refilled
-        }
-      }
+      TMR(4);
     }
+#ifdef FA_BWD_TIMERS
+    if (warp == 0 && lane == 0) {
+      for (int i = 0; i < 6; ++i) atomicAdd(&g_bwd_t[i], (unsigned long long)tm[i]);
+      atomicAdd(&g_bwd_t[7], (unsigned long long)iters);
+    }
+#endif
+    // every MMA of the CTA has completed once the last block's Q slot has been released
+    if (ok && iters > 0) ok = mbar_wait(bar_q_empty((iters - 1) % NSQ), ((iters - 1) / NSQ) & 1, W_B_QDO_EMPTY, abort_flag);
+    tc_fence_after();
 
-    if (lane == 0) bulk_wait_all();  // the dQ reductions of this warp have been performed
     // ---- epilogue: dK (scaled) and dV
     if (ok && *abort_flag == 0) {
       const uint32_t tdV = tmem + lane_off + C::COL_DV, tdK = tmem + lane_off + C::COL_DK;
@@ -326,8 +344,8 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
       }
     }
   } else {
-    setmaxnreg_dec<72>();
-    if (warp == 8) {
+    setmaxnreg_dec<kRegsOther>();
+    if (warp == kWarpProducer) {
       // -------------------------------------------------------------- TMA producer
       if (lane == 0 && run) {
         prefetch_tensormap(&P.tq);
@@ -341,101 +359,145 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
           tma_load_4d(sV + c * kChunkBytes, &P.tv, bar_kv, c * 64, (int)si.k_row0 + n0, hk, kb);
         }
         bool ok = true;
-        for (int it = 0; it < iters && ok; ++it) {
-          const int slot = it & 1, round = it >> 1;
-          ok = mbar_wait(bar_qdo_empty(slot), (round & 1) ^ 1, W_B_QDO_EMPTY, abort_flag);
+        Walk wk = walk0;
+        for (int it = 0; it < iters && ok; ++it, wk.next()) {
+          const int qs = it % NSQ, os = it % NSO;
+          const int row = (int)si.q_row0 + wk.mb * kB, hq = wk.hq;
+          ok = mbar_wait(bar_q_empty(qs), ((it / NSQ) & 1) ^ 1, W_B_QDO_EMPTY, abort_flag);
           if (!ok) break;
-          const int row = (int)si.q_row0 + mblk_of(it) * kB, hq = head_of(it);
-          mbar_expect_tx(bar_qdo_full(slot), 2 * C::TILE_BYTES);
-          for (int c = 0; c < C::NCHUNK; ++c) {
-            tma_load_4d(sQ(slot) + c * kChunkBytes, &P.tq, bar_qdo_full(slot), c * 64, row, hq, qb);
-            tma_load_4d(sDO(slot) + c * kChunkBytes, &P.tdo, bar_qdo_full(slot), c * 64, row, hq, qb);
-          }
+          mbar_expect_tx(bar_q_full(qs), C::TILE_BYTES);
+          for (int c = 0; c < C::NCHUNK; ++c) tma_load_4d(sQ(qs) + c * kChunkBytes, &P.tq, bar_q_full(qs), c * 64, row, hq, qb);
+          ok = mbar_wait(bar_do_empty(os), ((it / NSO) & 1) ^ 1, W_B_QDO_EMPTY, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(bar_do_full(os), C::TILE_BYTES);
+          for (int c = 0; c < C::NCHUNK; ++c) tma_load_4d(sDO(os) + c * kChunkBytes, &P.tdo, bar_do_full(os), c * 64, row, hq, qb);
         }
       }
-    } else if (warp == 10) {
+    } else if (warp == kWarpStats) {
       // -------------------------------------------------------------- LSE / D loader
+      // The values of the next block are fetched into registers before the wait for a free slot,
+      // so that the global-memory latency is not part of the hand-over.
       bool ok = run;
+      float l[4], d[4];
+      Walk wk = walk0;
+      auto fetch = [&]() {
+        const int m0 = wk.mb * kB, hq = wk.hq;
+        const float* lse_g = a.softmax_lse + ((int64_t)b * a.heads + hq) * a.lse_seqlen;
+        const float* d_g = a.softmax_d + ((int64_t)b * a.heads + hq) * a.d_seqlen;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int q = m0 + i * 32 + lane;
+          l[i] = q < si.sq ? lse_g[q] : INFINITY;
+          d[i] = q < si.sq ? d_g[q] : 0.f;
+        }
+      };
+      if (ok) fetch();
       for (int it = 0; it < iters && ok; ++it) {
         const int slot = it & 1, round = it >> 1;
         ok = mbar_wait(bar_st_empty(slot), (round & 1) ^ 1, W_B_STATS_EMPTY, abort_flag);
         if (!ok) break;
-        const int m0 = mblk_of(it) * kB, hq = head_of(it);
-        const float* lse_g = a.softmax_lse + ((int64_t)b * a.heads + hq) * a.lse_seqlen;
-        const float* d_g = a.softmax_d + ((int64_t)b * a.heads + hq) * a.d_seqlen;
         float* dst = sStats + slot * 256;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int r = i * 32 + lane, q = m0 + r;
-          const float l = q < si.sq ? lse_g[q] : INFINITY;
-          dst[r] = l * kLog2e;  // +inf stays +inf: exp2(x - inf) = 0 for rows without keys / past the end
-          dst[128 + r] = q < si.sq ? d_g[q] : 0.f;
+          dst[i * 32 + lane] = l[i] * kLog2e;  // +inf stays +inf: exp2(x - inf) = 0 for rows without keys / past the end
+          dst[128 + i * 32 + lane] = d[i];
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_st_full(slot));
+        if (it + 1 < iters) {
+          wk.next();
+          fetch();
+        }
       }
-    } else if (warp == 9) {
+    } else if (warp == kWarpMma) {
       // -------------------------------------------------------------- MMA issuer
+      // Order on the tensor pipe, block i:  S^T(i+1) | dV(i) | dK(i) dP^T(i+1)
+      //   S^T(i+1) is issued as soon as the compute warps hold S^T(i) in registers;
+      //   dV(i) waits for P^T(i), dK(i) for dS^T(i); both sit over dP^T(i), so dP^T(i+1) follows dK(i).
       if (lane == 0 && run) {
         constexpr int F = BFmt<T>::kIdesc;
         constexpr uint32_t idesc_st = make_idesc(kB, kB, F, 0, 0);   // S^T, dP^T: K-major x K-major, N = 128 queries
         constexpr uint32_t idesc_dv = make_idesc(kB, DH, F, 0, 1);   // dV, dK: A K-major (or TMEM), B MN-major, N = DH
-        constexpr uint32_t idesc_dq = make_idesc(kB, DH, F, 1, 1);   // dQ: A MN-major, B MN-major
-        bool ok = mbar_wait(bar_kv, 0, W_B_KV, abort_flag);
-        auto issue_st = [&](uint32_t d_col, uint32_t a_tile, uint32_t b_tile, uint32_t bar) {
+        // One descriptor is built (K tile, K-major); every other operand differs from it only in the
+        // low word: the address field (+ byte offset >> 4) and, for MN-major reads, the LBO field.
+        const uint64_t d_base = smem_desc_sw128(sK, 16, 1024);
+        const uint32_t d_lo = (uint32_t)d_base, d_hi = (uint32_t)(d_base >> 32);
+        auto dsc = [&](uint32_t lo_add) { return ((uint64_t)d_hi << 32) | (uint64_t)(d_lo + lo_add); };
+        constexpr uint32_t kMn = (uint32_t)((kChunkBytes - 16) >> 4) << 16;  // K-major -> MN-major (LBO = chunk stride)
+        constexpr uint32_t oK = 0, oV = (C::OFF_V - C::OFF_K) >> 4, oQ = (C::OFF_Q - C::OFF_K) >> 4,
+                           oDO = (C::OFF_DO - C::OFF_K) >> 4, kTile16 = C::TILE_BYTES >> 4;
+        auto koff = [](int kk) { return (uint32_t)(((kk >> 2) * kChunkBytes + (kk & 3) * 32) >> 4); };  // K-major k-step
+        auto moff = [](int kk) { return (uint32_t)((kk * 2048) >> 4) + kMn; };                          // MN-major k-step
+        auto issue_st = [&](uint32_t d_col, uint32_t a_lo, uint32_t b_lo, uint32_t bar) {
 #pragma unroll
-          for (int kk = 0; kk < DH / 16; ++kk) {
-            const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
-            mma_ss(tmem + d_col, smem_desc_sw128(a_tile + off, 16, 1024), smem_desc_sw128(b_tile + off, 16, 1024), idesc_st,
-                   kk > 0);
-          }
+          for (int kk = 0; kk < DH / 16; ++kk) mma_ss(tmem + d_col, dsc(a_lo + koff(kk)), dsc(b_lo + koff(kk)), idesc_st, kk > 0);
           tc_commit(bar);
         };
-        if (ok) ok = mbar_wait(bar_qdo_full(0), 0, W_B_QDO_FULL, abort_flag);
+        bool ok = mbar_wait(bar_kv, 0, W_B_KV, abort_flag);
+        if (ok) ok = mbar_wait(bar_q_full(0), 0, W_B_QDO_FULL, abort_flag);
         if (ok) {
           tc_fence_after();
-          issue_st(C::COL_S, sK, sQ(0), bar_s);
-          issue_st(C::COL_DP, sV, sDO(0), bar_dp);
+          issue_st(C::COL_S, oK, oQ, bar_s);
         }
-        for (int it = 0; it < iters && ok; ++it) {
-          const int slot = it & 1;
-          ok = mbar_wait(bar_pds, it & 1, W_B_PDS, abort_flag);
-          if (!ok) break;
+        if (ok) ok = mbar_wait(bar_do_full(0), 0, W_B_QDO_FULL, abort_flag);
+        if (ok) {
           tc_fence_after();
-          // dV += P^T dO
-#pragma unroll
-          for (int kk = 0; kk < kB / 16; ++kk)
-            mma_ts(tmem + C::COL_DV, tmem + C::COL_S + kk * 8, smem_desc_sw128(sDO(slot) + kk * 2048, kChunkBytes, 1024),
-                   idesc_dv, (it > 0) || kk > 0);
-          // dK += dS^T Q
-#pragma unroll
-          for (int kk = 0; kk < kB / 16; ++kk) {
-            const uint32_t aoff = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
-            if (!(P.debug & 16))
-            mma_ss(tmem + C::COL_DK, smem_desc_sw128(sDS + aoff, 16, 1024),
-                   smem_desc_sw128(sQ(slot) + kk * 2048, kChunkBytes, 1024), idesc_dv, (it > 0) || kk > 0);
-          }
-          // dQ = dS K  (over the dP^T columns, which the compute warps have consumed)
-#pragma unroll
-          for (int kk = 0; kk < kB / 16; ++kk)
-            if (!(P.debug & 8))
-            mma_ss(tmem + C::COL_DP, smem_desc_sw128(sDS + kk * 2048, kChunkBytes, 1024),
-                   smem_desc_sw128(sK + kk * 2048, kChunkBytes, 1024), idesc_dq, kk > 0);
-          tc_commit(bar_dq_full);
-          tc_commit(bar_qdo_empty(slot));
-          if (it + 1 < iters) {
-            const int ns = (it + 1) & 1;
-            ok = mbar_wait(bar_qdo_full(ns), ((it + 1) >> 1) & 1, W_B_QDO_FULL, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            issue_st(C::COL_S, sK, sQ(ns), bar_s);
-            // dP^T(it+1) lands on the columns that still hold dQ(it): wait until it has been drained
-            ok = mbar_wait(bar_dq_empty, it & 1, W_B_DQ_EMPTY, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            issue_st(C::COL_DP, sV, sDO(ns), bar_dp);
-          }
+          issue_st(C::COL_DP, oV, oDO, bar_dp);
         }
+#ifdef FA_BWD_TIMERS
+        long long tm[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
+#endif
+        for (int it = 0; it < iters && ok; ++it) {
+          const bool more = it + 1 < iters;
+          const int qs = it % NSQ, os = it % NSO, nqs = (it + 1) % NSQ, nos = (it + 1) % NSO;
+          if (more) {
+            // S^T(it) has been read into registers: S^T(it+1) runs while P^T(it) is being computed
+            ok = mbar_wait(bar_sread, it & 1, W_B_S, abort_flag);
+            if (!ok) break;
+            TMR(0);
+            ok = mbar_wait(bar_q_full(nqs), ((it + 1) / NSQ) & 1, W_B_QDO_FULL, abort_flag);
+            if (!ok) break;
+            TMR(1);
+            tc_fence_after();
+            issue_st(C::COL_S, oK, oQ + nqs * kTile16, bar_s);
+            TMR(2);
+          }
+          // P^T(it) is in TMEM over dP^T(it): dV += P^T dO (the warpgroups' halves sit at columns 0 and 64 of
+          // the dP^T range); that was the last use of this dO tile
+          ok = mbar_wait(bar_p, it & 1, W_B_PDS, abort_flag);
+          if (!ok) break;
+          TMR(3);
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < kB / 16; ++kk)
+            mma_ts(tmem + C::COL_DV, tmem + C::COL_DP + (kk >> 2) * 64 + (kk & 3) * 8, dsc(oDO + os * kTile16 + moff(kk)),
+                   idesc_dv, (it > 0) || kk > 0);
+          tc_commit(bar_do_empty(os));
+          TMR(4);
+          // dS^T(it) is in TMEM next to P^T(it) (columns 32 and 96 of the dP^T range): dK += dS^T Q, the last
+          // use of this Q tile; after it the next dP^T may overwrite the range
+          ok = mbar_wait(bar_ds, it & 1, W_B_PDS, abort_flag);
+          if (!ok) break;
+          TMR(5);
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < kB / 16; ++kk)
+            mma_ts(tmem + C::COL_DK, tmem + C::COL_DP + 32 + (kk >> 2) * 64 + (kk & 3) * 8, dsc(oQ + qs * kTile16 + moff(kk)),
+                   idesc_dv, (it > 0) || kk > 0);
+          tc_commit(bar_q_empty(qs));
+          TMR(6);
+          if (more) {
+            ok = mbar_wait(bar_do_full(nos), ((it + 1) / NSO) & 1, W_B_QDO_FULL, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_st(C::COL_DP, oV, oDO + nos * kTile16, bar_dp);
+          }
+          TMR(7);
+        }
+#ifdef FA_BWD_TIMERS
+        for (int i = 0; i < 8; ++i) atomicAdd(&g_bwd_t[8 + i], (unsigned long long)tm[i]);
+        atomicAdd(&g_bwd_t[16], (unsigned long long)iters);
+#endif
       }
     }
   }
@@ -450,19 +512,28 @@ __global__ void __launch_bounds__(384, 1) bwd_tc_kernel(const __grid_constant__ 
     }
     __syncthreads();
   }
-  if (warp == 11) tmem_dealloc(tmem, C::TMEM_COLS);
+  if (warp == kWarpStats) tmem_dealloc(tmem, C::TMEM_COLS);
 }
+
+#ifdef FA_BWD_TIMERS
+}  // namespace
+}  // namespace fa
+extern "C" void fa_bwd_timers(unsigned long long* out, int reset) {
+  cudaMemcpyFromSymbol(out, fa::g_bwd_t, sizeof(unsigned long long) * 32);
+  if (reset) {
+    unsigned long long z[32] = {};
+    cudaMemcpyToSymbol(fa::g_bwd_t, z, sizeof(z));
+  }
+}
+namespace fa {
+namespace {
+#endif
 
 template <typename T, int DH>
 int launch_bwd_tc(const FaBwdArgs& a, cudaStream_t st) {
   using C = BCfg<DH>;
   BwdTcParams P;
   P.a = a;
-  {
-    const char* dbg = getenv("FA_B200_DEBUG_BWD");
-    P.debug = dbg ? atoi(dbg) : 0;
-    P.dq_blocks = dq_blocks_per_unit(a.cu_seqlens_q != nullptr, a.seqlen_q, a.total_q, a.batch);
-  }
   const bool varlen = a.cu_seqlens_q != nullptr;
   const int64_t q_rows = varlen ? a.total_q : a.seqlen_q, k_rows = varlen ? a.total_k : a.seqlen_k;
   const int64_t nb = varlen ? 1 : a.batch;
@@ -481,7 +552,7 @@ int launch_bwd_tc(const FaBwdArgs& a, cudaStream_t st) {
     attr_set = true;
   }
   dim3 grid((a.seqlen_k + kB - 1) / kB, a.heads_k, a.batch);
-  kern<<<grid, 384, C::SMEM_BYTES, st>>>(P);
+  kern<<<grid, kThreads, C::SMEM_BYTES, st>>>(P);
   return fa_host::check_launch("bwd_tc_kernel");
 }
 
@@ -491,6 +562,9 @@ bool bwd_tc_eligible(const FaBwdArgs& a) {
   if (a.head_dim > 128 || a.p_dropout > 0.f) return false;
   if (a.seqlen_k <= 0 || a.seqlen_q <= 0) return false;
   if (!tma_compatible(a.q) || !tma_compatible(a.k) || !tma_compatible(a.v) || !tma_compatible(a.dout)) return false;
+  // the epilogues store 16 bytes at a time
+  if (!tma_compatible(a.dq)) return false;
+  if (!a.accumulate_dkv && (!tma_compatible(a.dk) || !tma_compatible(a.dv))) return false;
   if (a.head_dim % 8) return false;
   if (a.cu_seqlens_q && (a.total_q <= 0 || a.total_k <= 0)) return false;
   return encode_tiled_fn() != nullptr;
