@@ -349,9 +349,10 @@ def main():
     pk = peaks()
     tf_fwd = f_fwd / (ms_fwd * 1e-3) / 1e12
     tf_bwd = 2.5 * f_fwd / (ms_bwd * 1e-3) / 1e12
-    # the backward main loop is the dominant kernel of a step (its launch also covers the two small
-    # bandwidth kernels before and after it, a few percent of the time: see profiles/)
-    roofline = {"bound": "tensor", "kernel": "backward (dq_dk_dv main loop + dot_do_o + convert_dq)",
+    # the backward pass dominates a step: two tensor-core kernels of similar length (dK/dV per key
+    # block, dQ per query block) after one small bandwidth kernel (dot_do_o, a few percent: see
+    # profiles/).  FLOPs are the algorithmic 5 GEMMs; the two kernels execute 7 (S and dP twice).
+    roofline = {"bound": "tensor", "kernel": "backward (bwd_dot_do_o + bwd_tc_kernel [dK,dV] + bwd_dq_tc_kernel [dQ])",
                 "achieved": tf_bwd, "peak": pk["tflops_burst"], "unit": "TFLOP/s",
                 "frac": tf_bwd / pk["tflops_burst"], "traffic": None, "peak_source": pk["source"],
                 "forward": {"kernel": "fwd_tc_kernel", "achieved": tf_fwd, "frac": tf_fwd / pk["tflops_burst"],

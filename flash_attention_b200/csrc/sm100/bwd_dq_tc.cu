@@ -4,14 +4,14 @@
 // tensor memory, and walks every 128-key block those rows can see (bwd_tc.cu holds part 1, dK / dV,
 // and says why the pass is split).  Same math as the dQ half of compute_dq_dk_dv_1colblock
 // (csrc/flash_attn/src/flash_bwd_kernel.h:425-1112):
-//   S   = Q K^T           (lanes = queries, columns = keys)             SS MMA  -> TMEM tS[j & 1]
+//   S   = Q K^T           (lanes = queries, columns = keys)             SS MMA  -> TMEM tS
 //   dP  = dO V^T                                                         SS MMA  -> TMEM tdP
 //   P   = exp2(S*scale*log2e - LSE*log2e)             one thread per query row, stays in registers
-//   dS  = P o (dP - D)                                                   -> TMEM (16-bit, over tS[j & 1])
+//   dS  = P o (dP - D)                                                   -> TMEM (16-bit, buffer j & 1)
 //   dQ += dS K            A = dS from TMEM, B = K tile (MN-major)        -> TMEM tdQ
-// S is double-buffered, so S(j+1) is on the tensor pipe while block j is being exponentiated, and
-// dS(j) reuses the columns of S(j), which leaves the dP columns free for dP(j+1) as soon as dP(j)
-// has been read.
+// S and dP are consumed into registers as soon as they are complete, so the tensor pipe computes
+// S(j+1) and dP(j+1) while the compute warps are still working on block j; dS has two buffers of
+// its own, so dQ(j) never holds up either of them.
 //
 // Warps: 0-7 compute (warpgroup w handles key columns [64w, 64w+64) of the block; in the epilogue,
 // head-dim columns [D/2*w, ...)), 8 = TMA producer, 9 = MMA issuer, 10 = TMEM owner, 11 idle
@@ -52,7 +52,7 @@ struct QCfg {
   static constexpr int OFF_BAR = OFF_V + NSV * TILE_BYTES;
   static constexpr int NBAR = 2 * NSK + 2 * NSV + 8;
   static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16;
-  static constexpr int COL_S = 0, COL_DP = 256, COL_DQ = 384;  // S buffers at columns 0 and 128
+  static constexpr int COL_S = 0, COL_DP = 128, COL_DS = 256, COL_DQ = 384;  // dS: two 64-column buffers
   static constexpr int TMEM_COLS = 512;
 };
 
@@ -75,8 +75,13 @@ struct QFmt<__nv_bfloat16> {
 #ifdef FA_BWD_TIMERS
 __device__ unsigned long long g_dq_t[32];
 #define TMR(i) do { long long t_ = clock64(); tm[i] += t_ - tprev; tprev = t_; } while (0)
+__device__ long long g_trace[512];
+#define TRC(ev) do { if (trace_on && j >= 4 && j < 8) g_trace[(j - 4) * 16 + (ev)] = clock64(); } while (0)
+#define TRW(ev) do { if (trace_w && j >= 4 && j < 8) g_trace[64 + warp * 32 + (j - 4) * 8 + (ev)] = clock64(); } while (0)
 #else
 #define TMR(i) do {} while (0)
+#define TRC(ev) do {} while (0)
+#define TRW(ev) do {} while (0)
 #endif
 
 template <typename T, int DH>
@@ -95,11 +100,14 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
   auto bar_v_full = [&](int st) { return bar0 + 8 * (2 * NSK + st); };
   auto bar_v_empty = [&](int st) { return bar0 + 8 * (2 * NSK + NSV + st); };
   constexpr int kB0 = 2 * NSK + 2 * NSV;
-  auto bar_s = [&](int buf) { return bar0 + 8 * (kB0 + buf); };
-  const uint32_t bar_qdo = bar0 + 8 * (kB0 + 2), bar_dp = bar0 + 8 * (kB0 + 3), bar_ds = bar0 + 8 * (kB0 + 4),
-                 bar_done = bar0 + 8 * (kB0 + 5);
+  const uint32_t bar_s = bar0 + 8 * kB0, bar_sread = bar0 + 8 * (kB0 + 1), bar_qdo = bar0 + 8 * (kB0 + 2),
+                 bar_dp = bar0 + 8 * (kB0 + 3), bar_ds = bar0 + 8 * (kB0 + 4), bar_done = bar0 + 8 * (kB0 + 5),
+                 bar_dpread = bar0 + 8 * (kB0 + 6);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_BAR + C::NBAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_BAR + C::NBAR * 8 + 4);
+#ifdef FA_BWD_TIMERS
+  volatile long long* t_mark = reinterpret_cast<volatile long long*>(smem + C::OFF_BAR + C::NBAR * 8 + 8);
+#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hq = blockIdx.y, b = blockIdx.z;
@@ -128,8 +136,9 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
       mbar_init(bar_v_full(s), 1);
       mbar_init(bar_v_empty(s), 1);
     }
-    mbar_init(bar_s(0), 1);
-    mbar_init(bar_s(1), 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_sread, 8);
+    mbar_init(bar_dpread, 8);
     mbar_init(bar_qdo, 1);
     mbar_init(bar_dp, 1);
     mbar_init(bar_ds, 8);
@@ -157,6 +166,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tdP = tmem + lane_off + C::COL_DP + w * 64;
     bool ok = (*abort_flag == 0);  // with iters == 0 the loop is skipped and the epilogue writes zeros
+#ifdef FA_BWD_TIMERS
+    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0;
+    const bool trace_w = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+#endif
     // per-row statistics of the forward pass; +inf LSE (rows past the end or without keys) gives P = 0
     float lse2 = INFINITY, dsum = 0.f;
     if (qrow < si.sq) {
@@ -172,14 +185,19 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
 #endif
     for (int j = 0; j < iters && ok; ++j) {
       const int n0 = (n_lo + j) * kB;
-      const uint32_t tS = tmem + lane_off + C::COL_S + (j & 1) * 128 + w * 64;
+      const uint32_t tS = tmem + lane_off + C::COL_S + w * 64;
       const bool need_mask = (n0 + kB > si.sk) ||
                              (a.window_right >= 0 && n0 + kB - 1 > m0 + si.shift + a.window_right) ||
                              (a.window_left >= 0 && n0 < m0 + kB - 1 + si.shift - a.window_left);
       // ---- P = exp2(S * scale - LSE), 64 key columns per thread, kept in registers
-      ok = mbar_wait(bar_s(j & 1), (j >> 1) & 1, W_Q_S, abort_flag);
+      ok = mbar_wait(bar_s, j & 1, W_Q_S, abort_flag);
       if (!ok) break;
       TMR(0);
+      TRC(0);
+      TRW(0);
+#ifdef FA_BWD_TIMERS
+      if (j > 0) tm[4] += clock64() - *t_mark;
+#endif
       tc_fence_after();
       float p[64];
       {
@@ -187,6 +205,12 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
         tmem_ld32(tS, s0);
         tmem_ld32(tS + 32, s1);
         tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sread);  // S(j) is in registers: S(j+1) may overwrite it
+        TMR(5);
+        TRC(1);
+        TRW(1);
 #pragma unroll
         for (int c = 0; c < 64; ++c)
           p[c] = ex2(fmaf(__uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]), scale_log2, -lse2));
@@ -196,34 +220,46 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
 #pragma unroll
         for (int c = 0; c < 64; ++c) p[c] = (c >= c_lo && c <= c_hi) ? p[c] : 0.f;
       }
-      // ---- dS = P o (dP - D), 16-bit, over the first half of this warpgroup's S columns
+      // ---- dS = P o (dP - D), 16-bit, into this block's dS buffer
       TMR(1);
       ok = mbar_wait(bar_dp, j & 1, W_Q_DP, abort_flag);
       if (!ok) break;
       TMR(2);
+      TRC(2);
       tc_fence_after();
       {
         uint32_t d0[32], d1[32], pk[32];
         tmem_ld32(tdP, d0);
         tmem_ld32(tdP + 32, d1);
         tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_dpread);  // dP(j) is in registers: dP(j+1) may overwrite it
+        TRC(3);
 #pragma unroll
         for (int c = 0; c < 64; c += 2) {
           const float x0 = p[c] * (__uint_as_float(c < 32 ? d0[c & 31] : d1[c & 31]) - dsum);
           const float x1 = p[c + 1] * (__uint_as_float(c < 32 ? d0[(c + 1) & 31] : d1[(c + 1) & 31]) - dsum);
           pk[c >> 1] = Pack<T>::two(x0, x1);
         }
-        tmem_st32(tS, pk);
+        // the buffer held dS(j-2): dQ(j-2), whose commit releases that block's K tile, must have read it
+        if (j >= 2) {
+          ok = mbar_wait(bar_k_empty((j - 2) % NSK), ((j - 2) / NSK) & 1, W_Q_KV_EMPTY, abort_flag);
+          if (!ok) break;
+        }
+        tmem_st32(tmem + lane_off + C::COL_DS + (j & 1) * 64 + w * 32, pk);
       }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_ds);
       TMR(3);
+      TRC(4);
+      TRW(2);
     }
 #ifdef FA_BWD_TIMERS
     if (warp == 0 && lane == 0) {
-      for (int i = 0; i < 4; ++i) atomicAdd(&g_dq_t[i], (unsigned long long)tm[i]);
+      for (int i = 0; i < 6; ++i) atomicAdd(&g_dq_t[i], (unsigned long long)tm[i]);
       atomicAdd(&g_dq_t[7], (unsigned long long)iters);
     }
 #endif
@@ -277,7 +313,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
         }
         bool ok = true;
 #ifdef FA_BWD_TIMERS
-        long long tm[4] = {0, 0, 0, 0}, tprev = clock64();
+        long long tm[6] = {0, 0, 0, 0, 0, 0}, tprev = clock64();
 #endif
         for (int j = 0; j < iters && ok; ++j) {
           const int ks = j % NSK, vs = j % NSV;
@@ -294,17 +330,23 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
           TMR(2);
           mbar_expect_tx(bar_v_full(vs), C::TILE_BYTES);
           for (int c = 0; c < C::NCHUNK; ++c) tma_load_4d(sV(vs) + c * kChunkBytes, &P.tv, bar_v_full(vs), c * 64, row, hk, kb);
+#ifdef FA_BWD_TIMERS
+          TMR(3);
+          mbar_wait(bar_k_full(ks), (j / NSK) & 1, W_Q_KV_FULL, abort_flag);
+          { long long t_ = clock64(); tm[4] += t_ - tprev; tprev = t_; }
+          mbar_wait(bar_v_full(vs), (j / NSV) & 1, W_Q_KV_FULL, abort_flag);
+          { long long t_ = clock64(); tm[5] += t_ - tprev; tprev = t_; }
+#endif
         }
 #ifdef FA_BWD_TIMERS
-        for (int i = 0; i < 4; ++i) atomicAdd(&g_dq_t[16 + i], (unsigned long long)tm[i]);
+        for (int i = 0; i < 6; ++i) atomicAdd(&g_dq_t[16 + i], (unsigned long long)tm[i]);
 #endif
       }
     } else if (warp == kWarpMma) {
       // -------------------------------------------------------------- MMA issuer
-      // Order on the tensor pipe, block j:  S(j+1) | dP(j+1) dQ(j)
-      //   S(j+1) goes to the other S buffer as soon as its K tile has landed;
-      //   dP(j+1) and dQ(j) wait for dS(j), which also says that dP(j) has been read;
-      //   S(j+2) overwrites dS(j) and is issued after dQ(j), which reads it.
+      // Each MMA group is issued as soon as its inputs exist and its output columns are free:
+      //   S(j+1) once the compute warps hold S(j) in registers, dP(j+1) once they hold dP(j),
+      //   dQ(j) once dS(j) is in its buffer.
       if (lane == 0 && run) {
         constexpr int F = QFmt<T>::kIdesc;
         constexpr uint32_t idesc_s = make_idesc(kB, kB, F, 0, 0);   // S, dP: K-major x K-major, N = 128 keys
@@ -328,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
         if (ok) ok = mbar_wait(bar_k_full(0), 0, W_Q_KV_FULL, abort_flag);
         if (ok) {
           tc_fence_after();
-          issue_s(C::COL_S, oQ, oK, bar_s(0));
+          issue_s(C::COL_S, oQ, oK, bar_s);
         }
         if (ok) ok = mbar_wait(bar_v_full(0), 0, W_Q_KV_FULL, abort_flag);
         if (ok) {
@@ -338,40 +380,78 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
         }
 #ifdef FA_BWD_TIMERS
         long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
+        const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 #endif
+        int ks = 0, nks = 1 % NSK, nvs = 1 % NSV;  // ring positions of K(j), K(j+1), V(j+1)
+        uint32_t kph = 0, vph = (1 / NSV) & 1;      // phase of K(j+1)'s / V(j+1)'s full barrier
+        if (nks == 0) kph ^= 1;
+        // every barrier is tested one MMA group ahead of its use (see mbar_test)
+        uint32_t h_sread = mbar_test(bar_sread, 0), h_k = mbar_test(bar_k_full(nks), kph), h_dpread = 0, h_v = 0, h_ds = 0;
         for (int j = 0; j < iters && ok; ++j) {
           const bool more = j + 1 < iters;
-          const int ks = j % NSK, nks = (j + 1) % NSK, nvs = (j + 1) % NSV;
+          TRC(15);
           if (more) {
-            ok = mbar_wait(bar_k_full(nks), ((j + 1) / NSK) & 1, W_Q_KV_FULL, abort_flag);
+            ok = mbar_wait_probed(h_sread, bar_sread, j & 1, W_Q_S, abort_flag);
+            TMR(6);
+            TRC(8);
+            if (ok) ok = mbar_wait_probed(h_k, bar_k_full(nks), kph, W_Q_KV_FULL, abort_flag);
             if (!ok) break;
             TMR(0);
+            TRC(9);
             tc_fence_after();
-            issue_s(C::COL_S + ((j + 1) & 1) * 128, oQ, oK + nks * kTile16, bar_s((j + 1) & 1));
+            h_dpread = mbar_test(bar_dpread, j & 1);
+            h_v = mbar_test(bar_v_full(nvs), vph);
+            issue_s(C::COL_S, oQ, oK + nks * kTile16, bar_s);
             TMR(1);
-          }
-          ok = mbar_wait(bar_ds, j & 1, W_Q_DS, abort_flag);
-          if (!ok) break;
-          if (more) {
-            ok = mbar_wait(bar_v_full(nvs), ((j + 1) / NSV) & 1, W_Q_KV_FULL, abort_flag);
+            TRC(10);
+#ifdef FA_BWD_TIMERS
+            *t_mark = clock64();
+#endif
+            ok = mbar_wait_probed(h_dpread, bar_dpread, j & 1, W_Q_DP, abort_flag);
+            if (ok) ok = mbar_wait_probed(h_v, bar_v_full(nvs), vph, W_Q_KV_FULL, abort_flag);
             if (!ok) break;
-          }
-          TMR(2);
-          tc_fence_after();
-          if (more) {
+            TMR(2);
+            TRC(11);
+            tc_fence_after();
+            h_ds = mbar_test(bar_ds, j & 1);
             issue_s(C::COL_DP, oDO, oV + nvs * kTile16, bar_dp);
             tc_commit(bar_v_empty(nvs));
+            TMR(3);
+            TRC(12);
+          } else {
+            h_ds = mbar_test(bar_ds, j & 1);
           }
-          // dQ += dS K: the two warpgroups' halves of dS sit at columns 0 and 64 of this block's S buffer
+          ok = mbar_wait_probed(h_ds, bar_ds, j & 1, W_Q_DS, abort_flag);
+          if (!ok) break;
+          TMR(4);
+          TRC(13);
+          tc_fence_after();
+          const int ks_now = ks;
+          ks = nks;
+          if (++nks == NSK) {
+            nks = 0;
+            kph ^= 1;
+          }
+          if (++nvs == NSV) {
+            nvs = 0;
+            vph ^= 1;
+          }
+          if (j + 2 < iters) {
+            h_sread = mbar_test(bar_sread, (j + 1) & 1);
+            h_k = mbar_test(bar_k_full(nks), kph);
+          }
+          // dQ += dS K: the two warpgroups' halves of dS are the two 32-column halves of this block's buffer
 #pragma unroll
           for (int kk = 0; kk < kB / 16; ++kk)
-            mma_ts(tmem + C::COL_DQ, tmem + C::COL_S + (j & 1) * 128 + (kk >> 2) * 64 + (kk & 3) * 8,
-                   dsc(oK + ks * kTile16 + moff(kk)), idesc_dq, (j > 0) || kk > 0);
-          tc_commit(bar_k_empty(ks));
-          TMR(3);
+            mma_ts(tmem + C::COL_DQ, tmem + C::COL_DS + (j & 1) * 64 + kk * 8, dsc(oK + ks_now * kTile16 + moff(kk)), idesc_dq,
+                   (j > 0) || kk > 0);
+          tc_commit(bar_k_empty(ks_now));
+          TMR(5);
+          TRC(14);
         }
 #ifdef FA_BWD_TIMERS
-        for (int i = 0; i < 4; ++i) atomicAdd(&g_dq_t[8 + i], (unsigned long long)tm[i]);
+        for (int i = 0; i < 6; ++i) atomicAdd(&g_dq_t[8 + i], (unsigned long long)tm[i]);
+        atomicAdd(&g_dq_t[14], (unsigned long long)tm[6]);
         atomicAdd(&g_dq_t[15], (unsigned long long)iters);
 #endif
         if (ok) tc_commit(bar_done);
@@ -397,6 +477,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
 }  // namespace fa
 extern "C" void fa_bwd_dq_timers(unsigned long long* out, int reset) {
   cudaMemcpyFromSymbol(out, fa::g_dq_t, sizeof(unsigned long long) * 32);
+  if (reset == 2) cudaMemcpyFromSymbol(out, fa::g_trace, sizeof(long long) * 64);
+  if (reset == 3) cudaMemcpyFromSymbol(out, fa::g_trace, sizeof(long long) * 320);
   if (reset) {
     unsigned long long z[32] = {};
     cudaMemcpyToSymbol(fa::g_dq_t, z, sizeof(z));

@@ -328,62 +328,78 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
         constexpr uint32_t idesc_o = make_idesc(kBM, DH, Fmt<T>::kIdesc, 0, 1);
         bool ok = true;
         int p_iter[2] = {0, 0};  // softmax iterations consumed per tile
+        // One descriptor is built (Q tile 0, K-major); every other operand differs from it only in the
+        // low word: the address field (+ byte offset >> 4) and, for MN-major reads, the LBO field.
+        const uint64_t d_base = smem_desc_sw128(sQ, 16, 1024);
+        const uint32_t d_lo = (uint32_t)d_base, d_hi = (uint32_t)(d_base >> 32);
+        auto dsc = [&](uint32_t lo_add) { return ((uint64_t)d_hi << 32) | (uint64_t)(d_lo + lo_add); };
+        constexpr uint32_t kMn = (uint32_t)((kChunkBytes - 16) >> 4) << 16;  // K-major -> MN-major (LBO = chunk stride)
+        constexpr uint32_t kTile16 = C::TILE_BYTES >> 4, oKV = (2 * C::TILE_BYTES) >> 4;
         auto issue_s = [&](int t, int slot) {
           const uint32_t d = tmem + (t ? C::COL_S1 : C::COL_S0);
+          const uint32_t a_lo = t ? kTile16 : 0u, b_lo = oKV + slot * kTile16;
 #pragma unroll
           for (int kk = 0; kk < DH / 16; ++kk) {
-            const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
-            const uint64_t ad = smem_desc_sw128(sQ + t * C::TILE_BYTES + off, 16, 1024);
-            const uint64_t bd = smem_desc_sw128(sKV + slot * C::TILE_BYTES + off, 16, 1024);
-            mma_ss(d, ad, bd, idesc_s, kk > 0);
+            const uint32_t off = (uint32_t)(((kk >> 2) * kChunkBytes + (kk & 3) * 32) >> 4);
+            mma_ss(d, dsc(a_lo + off), dsc(b_lo + off), idesc_s, kk > 0);
           }
           tc_commit(bar_sfull(t));
         };
         auto issue_pv = [&](int t, int slot, bool first) {
           const uint32_t d = tmem + (t ? C::COL_O1 : C::COL_O0);
           const uint32_t pa = tmem + (t ? C::COL_S1 : C::COL_S0);
+          const uint32_t b_lo = oKV + slot * kTile16 + kMn;
 #pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) {
-            const uint64_t bd = smem_desc_sw128(sKV + slot * C::TILE_BYTES + kk * 2048, kChunkBytes, 1024);
-            mma_ts(d, pa + kk * 8, bd, idesc_o, (!first) || kk > 0);
-          }
+          for (int kk = 0; kk < kBN / 16; ++kk) mma_ts(d, pa + kk * 8, dsc(b_lo + (uint32_t)((kk * 2048) >> 4)), idesc_o, (!first) || kk > 0);
           tc_commit(bar_ofull(t));
         };
         auto in_range = [&](int t, int j) { return j >= lo[t] && j < hi[t]; };
         auto slot_of = [&](int idx) { return idx % C::STAGES; };
-        auto wait_full = [&](int idx) {
-          return mbar_wait(bar_full(slot_of(idx)), (idx / C::STAGES) & 1, W_KVFULL, abort_flag);
-        };
+        auto par_of = [&](int idx) { return (uint32_t)((idx / C::STAGES) & 1); };
         if (nblk > 0) {
           for (int t = 0; t < 2 && ok; ++t)
             if (hi[t] > lo[t]) ok = mbar_wait(bar_qfull(t), 0, W_QFULL, abort_flag);
           // prologue: S_t(J_lo)
-          if (ok) ok = wait_full(0);
+          if (ok) ok = mbar_wait(bar_full(slot_of(0)), par_of(0), W_KVFULL, abort_flag);
           if (ok) {
             tc_fence_after();
             for (int t = 0; t < 2; ++t)
               if (in_range(t, J_lo)) issue_s(t, slot_of(0));
             tc_commit(bar_empty(slot_of(0)));
           }
+          // Every barrier is tested one MMA group ahead of its use (see mbar_test): the answers for
+          // V(j), K(j+1) and tile 0's P are requested while tile 1's group of the block before is being
+          // issued, the answer for tile 1's P while tile 0's group is being issued.
+          uint32_t h_v = mbar_test(bar_full(slot_of(1)), par_of(1)), h_k = mbar_test(bar_full(slot_of(2)), par_of(2));
+          uint32_t h_p[2] = {mbar_test(bar_pfull(0), 0), 0};
           for (int j = J_lo; j < J_hi && ok; ++j) {
             const int iv = 2 * (j - J_lo) + 1;  // ring index of V(j)
             const int ik = iv + 1;              // ring index of K(j+1)
-            ok = wait_full(iv);
+            ok = mbar_wait_probed(h_v, bar_full(slot_of(iv)), par_of(iv), W_KVFULL, abort_flag);
             if (!ok) break;
             const bool more = j + 1 < J_hi;
             if (more) {
-              ok = wait_full(ik);
+              ok = mbar_wait_probed(h_k, bar_full(slot_of(ik)), par_of(ik), W_KVFULL, abort_flag);
               if (!ok) break;
             }
             tc_fence_after();
             for (int t = 0; t < 2 && ok; ++t) {
-              if (in_range(t, j)) {
-                ok = mbar_wait(bar_pfull(t), p_iter[t] & 1, W_PFULL, abort_flag);
+              const bool pv = in_range(t, j);
+              if (pv) {
+                ok = mbar_wait_probed(h_p[t], bar_pfull(t), p_iter[t] & 1, W_PFULL, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                issue_pv(t, slot_of(iv), j == lo[t]);
                 ++p_iter[t];
               }
+              // requests for the group after this one
+              if (t == 0) {
+                h_p[1] = mbar_test(bar_pfull(1), p_iter[1] & 1);
+              } else if (more) {
+                h_v = mbar_test(bar_full(slot_of(iv + 2)), par_of(iv + 2));
+                h_k = mbar_test(bar_full(slot_of(ik + 2)), par_of(ik + 2));
+                h_p[0] = mbar_test(bar_pfull(0), p_iter[0] & 1);
+              }
+              if (pv) issue_pv(t, slot_of(iv), j == lo[t]);
               if (t == 1) tc_commit(bar_empty(slot_of(iv)));
               if (more && in_range(t, j + 1)) issue_s(t, slot_of(ik));
               if (more && t == 1) tc_commit(bar_empty(slot_of(ik)));

@@ -56,6 +56,22 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
       : "memory");
   return ok != 0;
 }
+// Non-blocking test of a phase.  For a lone thread the round trip to the barrier is ~100+ cycles;
+// the MMA issuer tests the barrier of its NEXT group before it issues the current group's MMAs and
+// consumes the answer afterwards (mbar_wait_probed), so the tensor pipe is not left idle meanwhile.
+// A phase that has been seen complete stays complete until its barrier completes another phase,
+// which in these kernels needs further work of the testing thread itself.
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
 // Returns false (and records `code`) when the wait gave up or the kernel is already aborting.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code, volatile int* abort_flag,
                                           int mode = 0) {
@@ -78,6 +94,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
       }
     }
   }
+}
+
+__device__ __forceinline__ bool mbar_wait_probed(uint32_t hit, uint32_t bar, uint32_t parity, int code,
+                                                 volatile int* abort_flag) {
+  if (hit) return true;
+  return mbar_wait(bar, parity, code, abort_flag);
 }
 
 // ---- TMA -------------------------------------------------------------------------------------

@@ -2,7 +2,8 @@
 
 The reference has no multi-GPU attention (its kernels see the whole sequence of the local heads);
 this module adds the sequence-sharded case on top of the same kernels.  Rank r owns the rows
-[r*S/P, (r+1)*S/P) of q, k, v.  In step s it attends its queries to the K/V block that started on
+[r*S/P, (r+1)*S/P) of q, k, v (or, in the "zigzag" layout that balances a causal mask, chunks r and
+2P-1-r of 2P).  In step s it attends its queries to the K/V block that started on
 rank (r - s) mod P, while that block is already on its way to the next rank (NCCL send/recv over
 NVLink on a side stream, received into this GPU's own memory before any kernel reads it).
 Partial results are merged by their log-sum-exp, the same math as the split-KV combine
@@ -131,88 +132,153 @@ class _P2P:
             r.wait()
 
 
-def ring_forward(q, k, v, scale, causal, window_size, group=None, block_ops=CudaBlockOps):
+def layout_chunks(layout, rank, world, s_loc):
+    """Global (start, length) of the pieces of the sequence that `rank` holds, in local order.
+    "contiguous": rows [rank*s_loc, (rank+1)*s_loc).  "zigzag": the sequence is cut into 2*world
+    chunks and rank r holds chunks r and 2*world-1-r, which gives every rank the same amount of
+    visible (query, key) area under a causal mask in every step of the ring."""
+    if layout == "contiguous":
+        return [(rank * s_loc, s_loc)]
+    if layout == "zigzag":
+        if s_loc % 2:
+            raise ValueError("zigzag layout needs an even number of local rows")
+        c = s_loc // 2
+        return [(rank * c, c), ((2 * world - 1 - rank) * c, c)]
+    raise ValueError("unknown layout %r" % (layout,))
+
+
+def zigzag_shard(x, rank, world, dim=1):
+    """The rows of the full sequence `x` that `rank` holds in the zigzag layout."""
+    c = x.shape[dim] // (2 * world)
+    return torch.cat([x.narrow(dim, rank * c, c), x.narrow(dim, (2 * world - 1 - rank) * c, c)], dim=dim)
+
+
+def zigzag_unshard(shards, dim=1):
+    """Inverse of zigzag_shard over the list of all ranks' shards."""
+    world = len(shards)
+    c = shards[0].shape[dim] // 2
+    chunks = [None] * (2 * world)
+    for r, sh in enumerate(shards):
+        chunks[r] = sh.narrow(dim, 0, c)
+        chunks[2 * world - 1 - r] = sh.narrow(dim, c, c)
+    return torch.cat(chunks, dim=dim)
+
+
+def _split(x, chunks, dim=1):
+    out, off = [], 0
+    for _, n in chunks:
+        out.append(x.narrow(dim, off, n).contiguous())
+        off += n
+    return out
+
+
+def ring_forward(q, k, v, scale, causal, window_size, group=None, block_ops=CudaBlockOps, layout="contiguous"):
     """Forward of ring attention on this rank's shard. q: (B, S_loc, H, D); k, v: (B, S_loc, Hk, D).
-    Global sequence = concatenation of the shards in rank order.  Returns (out, lse) with lse fp32
-    (B, H, S_loc), +inf where a row sees no key."""
+    The global sequence is laid out over the ranks as `layout` says (layout_chunks).  Returns
+    (out, lse) with lse fp32 (B, H, S_loc), +inf where a row sees no key."""
     p2p = _P2P(group)
     P, r = p2p.world, p2p.rank
     S_loc = q.shape[1]
     window = _normalize_window(causal, window_size)
-    k_cur, v_cur = k.contiguous(), v.contiguous()
-    out_acc = lse_acc = None
+    mine = layout_chunks(layout, r, P, S_loc)
+    q_ch = _split(q, mine)
+    kv_cur = _split(k, mine) + _split(v, mine)  # [K chunks..., V chunks...]
+    n = len(mine)
+    acc = [None] * n
     for s in range(P):
         src = (r - s) % P
+        theirs = layout_chunks(layout, src, P, S_loc)
         reqs = None
         if s + 1 < P:
-            k_nxt, v_nxt = torch.empty_like(k_cur), torch.empty_like(v_cur)
-            reqs = p2p.start([k_cur, v_cur], [k_nxt, v_nxt])
-        if block_visible(r * S_loc, S_loc, src * S_loc, S_loc, window):
-            o, l = block_ops.fwd(q, k_cur, v_cur, scale, window, (r - src) * S_loc)
-            if out_acc is None:
-                out_acc, lse_acc = o.float(), torch.where(torch.isinf(l), torch.full_like(l, float("-inf")), l)
-            else:
-                out_acc, lse_acc = merge_partials(out_acc, lse_acc, o.float(), l)
+            kv_nxt = [torch.empty_like(t) for t in kv_cur]
+            reqs = p2p.start(kv_cur, kv_nxt)
+        for qi, (qg, qn) in enumerate(mine):
+            for ki, (kg, kn) in enumerate(theirs):
+                if not block_visible(qg, qn, kg, kn, window):
+                    continue
+                o, l = block_ops.fwd(q_ch[qi], kv_cur[ki], kv_cur[n + ki], scale, window, qg - kg)
+                if acc[qi] is None:
+                    acc[qi] = (o.float(), torch.where(torch.isinf(l), torch.full_like(l, float("-inf")), l))
+                else:
+                    acc[qi] = merge_partials(acc[qi][0], acc[qi][1], o.float(), l)
         if reqs is not None:
             p2p.finish(reqs)
-            k_cur, v_cur = k_nxt, v_nxt
-    if out_acc is None:
-        out_acc = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
-        lse_acc = torch.full((q.shape[0], q.shape[2], S_loc), float("-inf"), device=q.device)
+            kv_cur = kv_nxt
+    outs, lses = [], []
+    for qi, (qg, qn) in enumerate(mine):
+        if acc[qi] is None:
+            outs.append(torch.zeros(q_ch[qi].shape, dtype=torch.float32, device=q.device))
+            lses.append(torch.full((q.shape[0], q.shape[2], qn), float("-inf"), device=q.device))
+        else:
+            outs.append(acc[qi][0])
+            lses.append(acc[qi][1])
+    out_acc, lse_acc = torch.cat(outs, dim=1), torch.cat(lses, dim=-1)
     lse = torch.where(torch.isinf(lse_acc) & (lse_acc < 0), torch.full_like(lse_acc, float("inf")), lse_acc)
     return out_acc.to(q.dtype), lse
 
 
-def ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group=None, block_ops=CudaBlockOps):
+def ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group=None, block_ops=CudaBlockOps,
+                  layout="contiguous"):
     """Backward of ring attention.  Returns (dq, dk, dv) of this rank's shards."""
     p2p = _P2P(group)
     P, r = p2p.world, p2p.rank
     S_loc = q.shape[1]
     window = _normalize_window(causal, window_size)
-    k_cur, v_cur = k.contiguous(), v.contiguous()
-    dk_cur = torch.zeros(k.shape, dtype=torch.float32, device=k.device)
-    dv_cur = torch.zeros(v.shape, dtype=torch.float32, device=v.device)
-    dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
-    dout = dout.contiguous()
+    mine = layout_chunks(layout, r, P, S_loc)
+    n = len(mine)
+    q_ch, out_ch, do_ch = _split(q, mine), _split(out, mine), _split(dout, mine)
+    lse_ch = _split(lse, mine, dim=-1)
+    kv_cur = _split(k, mine) + _split(v, mine)
+    # fp32 accumulators of dK / dV travel with their K / V chunks
+    g_cur = [torch.zeros(t.shape, dtype=torch.float32, device=t.device) for t in kv_cur]
+    dq_ch = [torch.zeros(t.shape, dtype=torch.float32, device=t.device) for t in q_ch]
     for s in range(P):
         src = (r - s) % P
+        theirs = layout_chunks(layout, src, P, S_loc)
         reqs = None
         if s + 1 < P:  # K/V of the next step can already travel; dK/dV follow after this step's compute
-            k_nxt, v_nxt = torch.empty_like(k_cur), torch.empty_like(v_cur)
-            reqs = p2p.start([k_cur, v_cur], [k_nxt, v_nxt])
-        if block_visible(r * S_loc, S_loc, src * S_loc, S_loc, window):
-            dq += block_ops.bwd(dout, q, k_cur, v_cur, out, lse, dk_cur, dv_cur, scale, window, (r - src) * S_loc).float()
+            kv_nxt = [torch.empty_like(t) for t in kv_cur]
+            reqs = p2p.start(kv_cur, kv_nxt)
+        for qi, (qg, qn) in enumerate(mine):
+            for ki, (kg, kn) in enumerate(theirs):
+                if not block_visible(qg, qn, kg, kn, window):
+                    continue
+                dq_ch[qi] += block_ops.bwd(do_ch[qi], q_ch[qi], kv_cur[ki], kv_cur[n + ki], out_ch[qi], lse_ch[qi],
+                                           g_cur[ki], g_cur[n + ki], scale, window, qg - kg).float()
         if reqs is not None:
             p2p.finish(reqs)
         # pass the gradient accumulators of this block on (after P hops they are back home)
-        dk_nxt, dv_nxt = torch.empty_like(dk_cur), torch.empty_like(dv_cur)
-        p2p.finish(p2p.start([dk_cur, dv_cur], [dk_nxt, dv_nxt]))
-        dk_cur, dv_cur = dk_nxt, dv_nxt
+        g_nxt = [torch.empty_like(t) for t in g_cur]
+        p2p.finish(p2p.start(g_cur, g_nxt))
+        g_cur = g_nxt
         if s + 1 < P:
-            k_cur, v_cur = k_nxt, v_nxt
-    return dq.to(q.dtype), dk_cur.to(k.dtype), dv_cur.to(v.dtype)
+            kv_cur = kv_nxt
+    dq = torch.cat(dq_ch, dim=1)
+    dk, dv = torch.cat(g_cur[:n], dim=1), torch.cat(g_cur[n:], dim=1)
+    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
 
 
 class RingAttnFunc(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, softmax_scale, causal, window_size, group, block_ops):
+    def forward(ctx, q, k, v, softmax_scale, causal, window_size, group, block_ops, layout):
         if softmax_scale is None:
             softmax_scale = q.shape[-1] ** (-0.5)
-        out, lse = ring_forward(q, k, v, softmax_scale, causal, window_size, group, block_ops)
+        out, lse = ring_forward(q, k, v, softmax_scale, causal, window_size, group, block_ops, layout)
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.cfg = (softmax_scale, causal, window_size, group, block_ops)
+        ctx.cfg = (softmax_scale, causal, window_size, group, block_ops, layout)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse = ctx.saved_tensors
-        scale, causal, window_size, group, block_ops = ctx.cfg
-        dq, dk, dv = ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group, block_ops)
-        return dq, dk, dv, None, None, None, None, None
+        scale, causal, window_size, group, block_ops, layout = ctx.cfg
+        dq, dk, dv = ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group, block_ops, layout)
+        return dq, dk, dv, None, None, None, None, None, None
 
 
 def ring_flash_attn_func(q, k, v, softmax_scale=None, causal=False, window_size=(-1, -1), group=None,
-                         block_ops=CudaBlockOps):
-    """Attention over a sequence that is sharded across the ranks of `group` (contiguous shards in
-    rank order).  Same semantics as flash_attn_func on the gathered sequence (seqlen_q == seqlen_k)."""
-    return RingAttnFunc.apply(q, k, v, softmax_scale, causal, tuple(window_size), group, block_ops)
+                         block_ops=CudaBlockOps, layout="contiguous"):
+    """Attention over a sequence that is sharded across the ranks of `group`: contiguous shards in
+    rank order, or the load-balanced "zigzag" layout (see layout_chunks, zigzag_shard).  Same
+    semantics as flash_attn_func on the gathered sequence (seqlen_q == seqlen_k)."""
+    return RingAttnFunc.apply(q, k, v, softmax_scale, causal, tuple(window_size), group, block_ops, layout)

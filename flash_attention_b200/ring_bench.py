@@ -1,6 +1,7 @@
 """bench.py --workload ring: ONE long sequence (batch 1, seqlen 32768, 32 query heads, 8 KV heads,
 head_dim 128, bf16, causal) sharded by rows over the ranks with context-parallel ring attention.
-Strong scaling: the total work is fixed, every rank owns seqlen / N rows.  At N = 1 the ring has a
+Strong scaling: the total work is fixed, every rank owns seqlen / N rows (for N > 1 in the zigzag
+layout, which gives all ranks the same share of the causal mask).  At N = 1 the ring has a
 single step and is plain local attention.  FLOP model as in bench.py (fwd 4*S^2*H*D/2, bwd 2.5x).
 """
 import json
@@ -27,6 +28,7 @@ def main(args):
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     S, H, Hk, D = 32768, 32, 8, 128
     S_loc = S // world
+    layout = "zigzag" if world > 1 else "contiguous"  # balances the causal mask over the ranks
     g = torch.Generator(device=dev).manual_seed(2 + rank)
     q = torch.randn(1, S_loc, H, D, device=dev, dtype=torch.bfloat16, generator=g).requires_grad_(True)
     k = torch.randn(1, S_loc, Hk, D, device=dev, dtype=torch.bfloat16, generator=g).requires_grad_(True)
@@ -34,7 +36,7 @@ def main(args):
     do = torch.randn(1, S_loc, H, D, device=dev, dtype=torch.bfloat16, generator=g)
 
     def step():
-        out = ring_flash_attn_func(q, k, v, causal=True)
+        out = ring_flash_attn_func(q, k, v, causal=True, layout=layout)
         return torch.autograd.grad(out, (q, k, v), do)
 
     for _ in range(max(3, args.warmup)):
@@ -59,9 +61,9 @@ def main(args):
             "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOPS/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "ring_gqa_b1_s32768_h32_hk8_d128_causal", "rows_per_gpu": S_loc,
+            "config": {"workload": "ring_gqa_b1_s32768_h32_hk8_d128_causal", "rows_per_gpu": S_loc, "layout": layout,
                        "exchange": "K/V blocks by NCCL send/recv, dK/dV fp32 accumulators travel in the backward",
                        "l2": "inputs larger than L2"},
-            "gpu_launches": args.steps * 4 * ((world + 1) // 2 + 1), "device_status": status,
+            "gpu_launches": args.steps * 4 * (2 * world + 1 if world > 1 else 1), "device_status": status,
         }))
     dist.destroy_process_group()

@@ -18,7 +18,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, causal, window, out_q):
+def _worker(rank, world, port, causal, window, out_q, layout="contiguous"):
     import torch.distributed as dist
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -27,7 +27,7 @@ def _worker(rank, world, port, causal, window, out_q):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        from flash_attention_b200.ring import ring_flash_attn_func
+        from flash_attention_b200.ring import ring_flash_attn_func, zigzag_shard
         from oracle import attention_oracle as O
 
         g = torch.Generator().manual_seed(0)
@@ -36,11 +36,14 @@ def _worker(rank, world, port, causal, window, out_q):
         k = torch.randn(B, S, Hk, D, generator=g).bfloat16()
         v = torch.randn(B, S, Hk, D, generator=g).bfloat16()
         do = torch.randn(B, S, H, D, generator=g).bfloat16()
-        sl = slice(rank * S // world, (rank + 1) * S // world)
+        if layout == "zigzag":
+            shard = lambda x: zigzag_shard(x, rank, world)
+        else:
+            shard = lambda x: x[:, rank * S // world:(rank + 1) * S // world]
         dev = torch.device("cuda", rank)
-        ql, kl, vl = (x[:, sl].to(dev).requires_grad_(True) for x in (q, k, v))
-        out = ring_flash_attn_func(ql, kl, vl, causal=causal, window_size=window)
-        dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), do[:, sl].to(dev))
+        ql, kl, vl = (shard(x).to(dev).requires_grad_(True) for x in (q, k, v))
+        out = ring_flash_attn_func(ql, kl, vl, causal=causal, window_size=window, layout=layout)
+        dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), shard(do).to(dev))
         res = []
         for upcast in (True, False):
             qf, kf, vf = (x.to(dev).requires_grad_(True) for x in (q, k, v))
@@ -49,23 +52,24 @@ def _worker(rank, world, port, causal, window, out_q):
         truth, lowp = res
         errs = []
         for mine, t, l in zip((out.detach(), dq, dk, dv), truth, lowp):
-            e = (mine.float() - t[:, sl].float()).abs().max().item()
-            y = (l[:, sl].float() - t[:, sl].float()).abs().max().item()
+            e = (mine.float() - shard(t).float()).abs().max().item()
+            y = (shard(l).float() - shard(t).float()).abs().max().item()
             errs.append((e, y))
         out_q.put((rank, errs))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("causal,window", [(True, (-1, -1)), (False, (-1, -1)), (False, (300, 0))])
-def test_ring_attention_two_gpus(causal, window):
+@pytest.mark.parametrize("causal,window,layout", [(True, (-1, -1), "contiguous"), (False, (-1, -1), "contiguous"),
+                                                  (False, (300, 0), "contiguous"), (True, (-1, -1), "zigzag")])
+def test_ring_attention_two_gpus(causal, window, layout):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     world = 2
     ctx = mp.get_context("spawn")
     out_q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, causal, window, out_q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, causal, window, out_q, layout)) for r in range(world)]
     for p in procs:
         p.start()
     results = [out_q.get(timeout=300) for _ in range(world)]

@@ -70,7 +70,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, causal, window, out_q):
+def _worker(rank, world, port, causal, window, out_q, layout="contiguous"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -83,15 +83,20 @@ def _worker(rank, world, port, causal, window, out_q):
         k = torch.randn(B, S, Hk, D, generator=g)
         v = torch.randn(B, S, Hk, D, generator=g)
         do = torch.randn(B, S, H, D, generator=g)
-        sl = slice(rank * S // world, (rank + 1) * S // world)
-        ql, kl, vl = (x[:, sl].clone().requires_grad_(True) for x in (q, k, v))
-        out = ring_flash_attn_func(ql, kl, vl, causal=causal, window_size=window, block_ops=OracleBlockOps)
-        dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), do[:, sl])
+        from flash_attention_b200.ring import zigzag_shard
+
+        if layout == "zigzag":
+            shard = lambda x: zigzag_shard(x, rank, world)
+        else:
+            shard = lambda x: x[:, rank * S // world:(rank + 1) * S // world]
+        ql, kl, vl = (shard(x).clone().requires_grad_(True) for x in (q, k, v))
+        out = ring_flash_attn_func(ql, kl, vl, causal=causal, window_size=window, block_ops=OracleBlockOps, layout=layout)
+        dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), shard(do))
         qf, kf, vf = (x.clone().requires_grad_(True) for x in (q, k, v))
         ref, _ = O.attention_oracle(qf, kf, vf, causal=causal, window_size=window)
         rdq, rdk, rdv = torch.autograd.grad(ref, (qf, kf, vf), do)
-        errs = [(out - ref[:, sl]).abs().max().item(), (dq - rdq[:, sl]).abs().max().item(),
-                (dk - rdk[:, sl]).abs().max().item(), (dv - rdv[:, sl]).abs().max().item()]
+        errs = [(out - shard(ref)).abs().max().item(), (dq - shard(rdq)).abs().max().item(),
+                (dk - shard(rdk)).abs().max().item(), (dv - shard(rdv)).abs().max().item()]
         out_q.put((rank, errs))
     finally:
         dist.destroy_process_group()
@@ -112,6 +117,39 @@ def test_ring_matches_full_attention(world, causal, window):
         assert p.exitcode == 0
     for rank, errs in results:
         assert max(errs) < 1e-4, (rank, errs)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("causal,window", [(True, (-1, -1)), (False, (9, 5))])
+def test_zigzag_ring_matches_full_attention(world, causal, window):
+    ctx = mp.get_context("spawn")
+    out_q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, causal, window, out_q, "zigzag")) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [out_q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, errs in results:
+        assert max(errs) < 1e-4, (rank, errs)
+
+
+def test_zigzag_shard_roundtrip_and_balance():
+    from flash_attention_b200.ring import block_visible, layout_chunks, zigzag_shard, zigzag_unshard
+
+    x = torch.arange(2 * 48 * 3).view(2, 48, 3)
+    for world in (2, 4):
+        assert torch.equal(zigzag_unshard([zigzag_shard(x, r, world) for r in range(world)]), x)
+        # under a causal mask every rank sees the same number of (query chunk, key chunk) pairs per step,
+        # except the step with its own keys (two diagonal blocks instead of one full block)
+        for step in range(1, world):
+            counts = []
+            for r in range(world):
+                mine, theirs = layout_chunks("zigzag", r, world, 12), layout_chunks("zigzag", (r - step) % world, world, 12)
+                counts.append(sum(block_visible(qg, qn, kg, kn, (-1, 0)) for qg, qn in mine for kg, kn in theirs))
+            assert counts == [2] * world, counts
 
 
 def test_merge_partials_matches_oracle():
