@@ -31,6 +31,10 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the two tensor-core backward kernels, per launch pair, from the ncu
+# capture summarised in profiles/ (bwd_tc_kernel 781.6 MB + bwd_dq_tc_kernel 660.7 MB; algorithmic bytes: 1479 MB)
+NCU_DRAM_BYTES_PER_BACKWARD = {"train_b16_s2048_h16_d128_causal": 1.4423e9}
+
 WORKLOADS = {
     # name: (batch, seqlen, heads, heads_k, head_dim, causal, dtype)
     "train_b16_s2048_h16_d128_causal": (16, 2048, 16, 16, 128, True, torch.bfloat16),
@@ -354,7 +358,7 @@ def main():
     # profiles/).  FLOPs are the algorithmic 5 GEMMs; the two kernels execute 7 (S and dP twice).
     roofline = {"bound": "tensor", "kernel": "backward (bwd_dot_do_o + bwd_tc_kernel [dK,dV] + bwd_dq_tc_kernel [dQ])",
                 "achieved": tf_bwd, "peak": pk["tflops_burst"], "unit": "TFLOP/s",
-                "frac": tf_bwd / pk["tflops_burst"], "traffic": None, "peak_source": pk["source"],
+                "frac": tf_bwd / pk["tflops_burst"], "traffic": NCU_DRAM_BYTES_PER_BACKWARD.get(wl), "peak_source": pk["source"],
                 "forward": {"kernel": "fwd_tc_kernel", "achieved": tf_fwd, "frac": tf_fwd / pk["tflops_burst"],
                             "frac_of_sustained": tf_fwd / pk["tflops_sustained"]},
                 "frac_of_sustained": tf_bwd / pk["tflops_sustained"]}
