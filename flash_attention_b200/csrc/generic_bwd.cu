@@ -18,42 +18,55 @@ namespace fa {
 
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(128) bwd_dot_do_o_kernel(const __grid_constant__ FaBwdArgs p, const int zero_dq) {
-  // one warp per query row; grid (ceil(max_sq/4), heads, batch).  zero_dq = 0 when the accumulator is
-  // the blocked one of the tensor-core path, which the host clears with a memset.
-  const int lane = threadIdx.x & 31;
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+__global__ void __launch_bounds__(256) bwd_dot_do_o_kernel(const __grid_constant__ FaBwdArgs p, const int zero_dq,
+                                                           const int tpr_log2) {
+  // Pure streaming: tpr = 2^tpr_log2 >= D/8 threads share a row, 16 bytes of O and of dO each; a CTA
+  // covers kRows rows in passes of 256/tpr rows, four passes in flight per thread.  Grid
+  // (ceil(max_sq/kRows), heads, batch).  zero_dq = 0 when the caller needs no cleared accumulator.
+  constexpr int kRows = 128;
+  const int tpr = 1 << tpr_log2;
+  const int sub = threadIdx.x & (tpr - 1);       // which 16-byte piece of the row
+  const int r_in_pass = threadIdx.x >> tpr_log2;  // row within a pass
+  const int rows_per_pass = 256 >> tpr_log2;
   const int h = blockIdx.y, b = blockIdx.z;
   const SeqInfo si = seq_info(p.cu_seqlens_q, p.cu_seqlens_k, nullptr, nullptr, p.seqlen_q, p.seqlen_k,
                               p.use_mask_shift, p.mask_shift, b);
   const int D = p.head_dim;
+  const int c = sub * 8;
+  const bool col_ok = c < D;
   float* dsum = p.softmax_d + ((int64_t)b * p.heads + h) * p.d_seqlen;
-  if (row >= si.sq) {
-    if (row < p.d_seqlen && lane == 0) dsum[row] = 0.f;
-    return;
-  }
-  const T* og = reinterpret_cast<const T*>(p.out.ptr) + si.q_batch * p.out.stride_b +
-                (si.q_row0 + row) * p.out.stride_s + (int64_t)h * p.out.stride_h;
-  const T* dog = reinterpret_cast<const T*>(p.dout.ptr) + si.q_batch * p.dout.stride_b +
-                 (si.q_row0 + row) * p.dout.stride_s + (int64_t)h * p.dout.stride_h;
-  // dq_accum is (batch, seqlen_q, heads, D) or packed (total_q, heads, D), fp32
-  float* dqa = p.dq_accum + ((si.q_batch * (int64_t)p.seqlen_q + si.q_row0 + row) * p.heads + h) * D;
-  float acc = 0.f;
-  for (int c = lane * 8; c < D; c += 256) {
-    uint4 a = *reinterpret_cast<const uint4*>(og + c);
-    uint4 d = *reinterpret_cast<const uint4*>(dog + c);
-    acc += Pack<T>::lo(a.x) * Pack<T>::lo(d.x) + Pack<T>::hi(a.x) * Pack<T>::hi(d.x);
-    acc += Pack<T>::lo(a.y) * Pack<T>::lo(d.y) + Pack<T>::hi(a.y) * Pack<T>::hi(d.y);
-    acc += Pack<T>::lo(a.z) * Pack<T>::lo(d.z) + Pack<T>::hi(a.z) * Pack<T>::hi(d.z);
-    acc += Pack<T>::lo(a.w) * Pack<T>::lo(d.w) + Pack<T>::hi(a.w) * Pack<T>::hi(d.w);
-    if (zero_dq) {
-      *reinterpret_cast<float4*>(dqa + c) = make_float4(0.f, 0.f, 0.f, 0.f);
-      *reinterpret_cast<float4*>(dqa + c + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+  const T* obase = reinterpret_cast<const T*>(p.out.ptr) + si.q_batch * p.out.stride_b + (int64_t)h * p.out.stride_h + c;
+  const T* dobase = reinterpret_cast<const T*>(p.dout.ptr) + si.q_batch * p.dout.stride_b + (int64_t)h * p.dout.stride_h + c;
+  const int row0 = blockIdx.x * kRows;
+  for (int base = 0; base < kRows; base += 4 * rows_per_pass) {
+    uint4 a[4], d[4];
+    int row[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      row[u] = row0 + base + u * rows_per_pass + r_in_pass;
+      const bool ok = col_ok && row[u] < si.sq;
+      a[u] = d[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (ok) {
+        a[u] = *reinterpret_cast<const uint4*>(obase + (si.q_row0 + row[u]) * p.out.stride_s);
+        d[u] = *reinterpret_cast<const uint4*>(dobase + (si.q_row0 + row[u]) * p.dout.stride_s);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float acc = Pack<T>::lo(a[u].x) * Pack<T>::lo(d[u].x) + Pack<T>::hi(a[u].x) * Pack<T>::hi(d[u].x);
+      acc += Pack<T>::lo(a[u].y) * Pack<T>::lo(d[u].y) + Pack<T>::hi(a[u].y) * Pack<T>::hi(d[u].y);
+      acc += Pack<T>::lo(a[u].z) * Pack<T>::lo(d[u].z) + Pack<T>::hi(a[u].z) * Pack<T>::hi(d[u].z);
+      acc += Pack<T>::lo(a[u].w) * Pack<T>::lo(d[u].w) + Pack<T>::hi(a[u].w) * Pack<T>::hi(d[u].w);
+      for (int o = tpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (sub == 0 && row[u] < p.d_seqlen) dsum[row[u]] = row[u] < si.sq ? acc : 0.f;
+      if (zero_dq && col_ok && row[u] < si.sq) {
+        // dq_accum is (batch, seqlen_q, heads, D) or packed (total_q, heads, D), fp32
+        float* dqa = p.dq_accum + ((si.q_batch * (int64_t)p.seqlen_q + si.q_row0 + row[u]) * p.heads + h) * D + c;
+        *reinterpret_cast<float4*>(dqa) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(dqa + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) dsum[row] = acc;
 }
 
 template <typename T>
@@ -362,8 +375,10 @@ static int launch_bwd_generic(const FaBwdArgs& a, cudaStream_t st) {
 template <typename T>
 int bwd_pre_t(const FaBwdArgs& a, int zero_dq, cudaStream_t st) {
   int rows = a.d_seqlen > a.seqlen_q ? a.d_seqlen : a.seqlen_q;
-  dim3 grid((rows + 3) / 4, a.heads, a.batch);
-  bwd_dot_do_o_kernel<T><<<grid, 128, 0, st>>>(a, zero_dq);
+  int tpr_log2 = 0;
+  while ((8 << tpr_log2) < a.head_dim) ++tpr_log2;  // threads per row: a power of two >= head_dim / 8 (<= 32)
+  dim3 grid((rows + 127) / 128, a.heads, a.batch);
+  bwd_dot_do_o_kernel<T><<<grid, 256, 0, st>>>(a, zero_dq, tpr_log2);
   return fa_host::check_launch("bwd_dot_do_o_kernel");
 }
 template <typename T>
