@@ -85,14 +85,16 @@ typedef struct FaFwdArgs {
 
 /* Backward.  Replaces mha_bwd (flash_api.cpp:609-811) and mha_varlen_bwd (flash_api.cpp:813-1036),
    i.e. the three launches dot_do_o -> dq_dk_dv -> convert_dq of
-   csrc/flash_attn/src/flash_bwd_launch_template.h:47-90. */
+   csrc/flash_attn/src/flash_bwd_launch_template.h:47-90.  For head dims up to 128 without dropout the
+   launches are dot_do_o -> dK/dV kernel -> dQ kernel instead: dq is written directly, without
+   atomics, and dq_accum is not touched. */
 typedef struct FaBwdArgs {
   FaTensor q, k, v, out, dout, dq, dk, dv;
   const float* softmax_lse; /* from the forward, same layout */
   int32_t lse_seqlen;
   float* softmax_d;         /* (batch, heads, d_seqlen) fp32 out: rowsum(dO * O) */
   int32_t d_seqlen;         /* row pitch of softmax_d (seqlen_q rounded up to 128) */
-  float* dq_accum;          /* fp32 workspace, fa_bwd_workspace_bytes() bytes, need not be zeroed */
+  float* dq_accum;          /* fp32 workspace, fa_bwd_workspace_bytes() bytes, need not be zeroed (used by the any-shape kernel) */
   int32_t batch, seqlen_q, seqlen_k, heads, heads_k, head_dim;
   int32_t dtype;
   float softmax_scale;
