@@ -91,7 +91,7 @@ class FaKvcacheArgs(C.Structure):
 EXPORTS = (
     "fa_fwd", "fa_bwd", "fa_fwd_kvcache", "fa_fwd_num_splits", "fa_kvcache_plan", "fa_bwd_workspace_bytes",
     "fa_combine", "fa_last_error", "fa_build_info", "fa_device_status", "fa_abi_struct_size",
-    "fa_fwd_kvcache_noalloc", "fa_noalloc_scratch_bytes",
+    "fa_fwd_kvcache_noalloc", "fa_noalloc_scratch_bytes", "fa_merge_partial",
 )
 
 _lib = None
@@ -124,6 +124,9 @@ def lib():
         L.fa_bwd_workspace_bytes.restype = c_i64
         L.fa_combine.argtypes = [c_vp, c_vp, c_vp, c_vp, c_i32, c_i64, c_i32, c_i64, c_i32, c_vp]
         L.fa_combine.restype = C.c_int
+        L.fa_merge_partial.argtypes = [C.POINTER(FaTensor), c_vp, c_i64, c_i64, C.POINTER(FaTensor), c_vp, c_i64, c_i64,
+                                       c_i32, c_i32, c_i32, c_i32, c_i32, c_vp]
+        L.fa_merge_partial.restype = C.c_int
         L.fa_last_error.restype = C.c_char_p
         L.fa_build_info.restype = C.c_char_p
         L.fa_device_status.restype = C.c_int

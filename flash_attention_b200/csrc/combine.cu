@@ -90,4 +90,69 @@ int combine(const float* out_parts, const float* lse_parts, const FaTensor& out,
   return fa_host::check_launch("combine_kernel");
 }
 
+// ---------------------------------------------------------------------------------------------
+// In-place merge of one more partial result into a running fp32 accumulator (the per-step update of
+// context-parallel ring attention): acc <- acc * exp(la - l) + part * exp(lb - l), la <- l, with
+// l = logaddexp(la, lb).  An LSE of +inf (the kernels' "row saw no key") or -inf means empty.
+struct MergeParams {
+  float* acc;
+  float* lse_acc;
+  const void* part;
+  const float* lse_part;
+  int64_t acc_sb, acc_ss, acc_sh, part_sb, part_ss, part_sh;
+  int64_t lacc_sb, lacc_sh, lpart_sb, lpart_sh;
+  int32_t B, S, H, D;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) merge_partial_kernel(const MergeParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = (int64_t)p.B * p.S * p.H;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int h = (int)(row % p.H);
+  const int s = (int)((row / p.H) % p.S);
+  const int b = (int)(row / ((int64_t)p.H * p.S));
+  float* la_p = p.lse_acc + b * p.lacc_sb + h * p.lacc_sh + s;
+  float la = *la_p, lb = p.lse_part[b * p.lpart_sb + h * p.lpart_sh + s];
+  if (la == INFINITY) la = -INFINITY;
+  if (lb == INFINITY) lb = -INFINITY;
+  const float mx = fmaxf(la, lb);
+  float wa = 0.f, wb = 0.f, l = -INFINITY;
+  if (mx != -INFINITY) {
+    const float ea = __expf(la - mx), eb = __expf(lb - mx);
+    const float inv = 1.f / (ea + eb);
+    wa = ea * inv;
+    wb = eb * inv;
+    l = mx + __logf(ea + eb);
+  }
+  float* a = p.acc + b * p.acc_sb + s * p.acc_ss + h * p.acc_sh;
+  const T* o = reinterpret_cast<const T*>(p.part) + b * p.part_sb + s * p.part_ss + h * p.part_sh;
+  for (int c = lane * 4; c < p.D; c += 128) {
+    float4 x = *reinterpret_cast<float4*>(a + c);
+    const uint2 y = *reinterpret_cast<const uint2*>(o + c);
+    x.x = wa * x.x + wb * Pack<T>::lo(y.x);
+    x.y = wa * x.y + wb * Pack<T>::hi(y.x);
+    x.z = wa * x.z + wb * Pack<T>::lo(y.y);
+    x.w = wa * x.w + wb * Pack<T>::hi(y.y);
+    *reinterpret_cast<float4*>(a + c) = x;
+  }
+  if (lane == 0) *la_p = l;
+}
+
+int merge_partial(const FaTensor& acc, float* lse_acc, int64_t lacc_sb, int64_t lacc_sh, const FaTensor& part,
+                  const float* lse_part, int64_t lpart_sb, int64_t lpart_sh, int B, int S, int H, int D, int dtype,
+                  cudaStream_t st) {
+  MergeParams p{reinterpret_cast<float*>(acc.ptr), lse_acc, part.ptr, lse_part, acc.stride_b, acc.stride_s, acc.stride_h,
+                part.stride_b, part.stride_s, part.stride_h, lacc_sb, lacc_sh, lpart_sb, lpart_sh, B, S, H, D};
+  const int64_t rows = (int64_t)p.B * p.S * p.H;
+  if (rows == 0) return 0;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (dtype == FA_DTYPE_BF16)
+    merge_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  else
+    merge_partial_kernel<__half><<<grid, 256, 0, st>>>(p);
+  return fa_host::check_launch("merge_partial_kernel");
+}
+
 }  // namespace fa

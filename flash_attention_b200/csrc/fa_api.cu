@@ -15,6 +15,9 @@ int bwd_pre(const FaBwdArgs& a, int zero_dq, cudaStream_t st);
 int bwd_post(const FaBwdArgs& a, cudaStream_t st);
 int bwd_post_blocked(const FaBwdArgs& a, int dhp, cudaStream_t st);
 int bwd_generic_main(const FaBwdArgs& a, cudaStream_t st);
+int merge_partial(const FaTensor& acc, float* lse_acc, int64_t lacc_sb, int64_t lacc_sh, const FaTensor& part,
+                  const float* lse_part, int64_t lpart_sb, int64_t lpart_sh, int B, int S, int H, int D, int dtype,
+                  cudaStream_t st);
 int combine(const float* out_parts, const float* lse_parts, const FaTensor& out, float* lse, int lse_pitch, int n_parts,
             int B, int H, int S, int D, int dtype, cudaStream_t st);
 int kvcache_prep(const FaKvcacheArgs& a, int q_follows_rows, cudaStream_t st);
@@ -96,7 +99,7 @@ const char* fa_last_error(void) { return fa_host::g_err; }
 
 const char* fa_build_info(void) {
   return "libfa_b200 arch=sm_100a kernels=fwd_tc(tcgen05+TMA),bwd_dkdv_tc(tcgen05+TMA),bwd_dq_tc(tcgen05+TMA),decode_splitkv(TMA),"
-         "fwd_generic(mma.sync),bwd_generic(mma.sync),combine,bwd_dot_do_o,bwd_convert_dq,kvcache_prep";
+         "fwd_generic(mma.sync),bwd_generic(mma.sync),combine,merge_partial,bwd_dot_do_o,bwd_convert_dq,kvcache_prep";
 }
 
 int fa_device_status(void) {
@@ -346,6 +349,21 @@ int fa_combine(const float* out_parts, const float* lse_parts, void* out, float*
   FaTensor o{out, 0, out_row_stride, 0};
   return fa::combine(out_parts, lse_parts, o, lse, (int)rows, n_parts, 1, 1, (int)rows, head_dim, dtype,
                      reinterpret_cast<cudaStream_t>(stream));
+}
+
+int fa_merge_partial(const FaTensor* acc, float* lse_acc, int64_t lse_acc_stride_b, int64_t lse_acc_stride_h,
+                     const FaTensor* part, const float* lse_part, int64_t lse_part_stride_b, int64_t lse_part_stride_h,
+                     int32_t batch, int32_t seqlen, int32_t heads, int32_t head_dim, int32_t dtype, fa_stream_t stream) {
+  FA_REQUIRE(acc && part && acc->ptr && part->ptr && lse_acc && lse_part, "null pointer");
+  FA_REQUIRE(dtype == FA_DTYPE_FP16 || dtype == FA_DTYPE_BF16, "FlashAttention only support fp16 and bf16 data type");
+  FA_REQUIRE(batch >= 0 && seqlen >= 0 && heads > 0, "bad sizes");
+  FA_REQUIRE(head_dim % 8 == 0 && head_dim > 0 && head_dim <= 256, "head_dim must be a multiple of 8, at most 256");
+  FA_REQUIRE((reinterpret_cast<uintptr_t>(acc->ptr) & 15) == 0 && (reinterpret_cast<uintptr_t>(part->ptr) & 7) == 0 &&
+                 acc->stride_s % 4 == 0 && acc->stride_h % 4 == 0 && acc->stride_b % 4 == 0 && part->stride_s % 4 == 0 &&
+                 part->stride_h % 4 == 0 && part->stride_b % 4 == 0,
+             "accumulator rows must be 16-byte aligned, partial rows 8-byte aligned");
+  return fa::merge_partial(*acc, lse_acc, lse_acc_stride_b, lse_acc_stride_h, *part, lse_part, lse_part_stride_b,
+                           lse_part_stride_h, batch, seqlen, heads, head_dim, dtype, reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

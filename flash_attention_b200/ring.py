@@ -63,7 +63,7 @@ class CudaBlockOps:
         dq_accum = torch.empty(lib().fa_bwd_workspace_bytes(B, Sq, H, D, 0, 0) // 4, dtype=torch.float32, device=q.device)
         a = FaBwdArgs()
         a.q, a.k, a.v, a.out, a.dout, a.dq = (tensor3(x) for x in (q, k, v, out, dout, dq))
-        a.softmax_lse, a.lse_seqlen = ptr(lse), lse.shape[-1]
+        a.softmax_lse, a.lse_seqlen = ptr(lse), lse.stride(1)  # row pitch: lse may be a column range of a wider tensor
         a.softmax_d, a.d_seqlen, a.dq_accum = ptr(softmax_d), d_seqlen, ptr(dq_accum)
         a.batch, a.seqlen_q, a.seqlen_k, a.heads, a.heads_k, a.head_dim = B, Sq, Sk, H, Hk, D
         a.dtype = _lib.FA_DTYPE_BF16 if q.dtype == torch.bfloat16 else _lib.FA_DTYPE_FP16
@@ -75,6 +75,23 @@ class CudaBlockOps:
         with torch.cuda.device(q.device):
             check(lib().fa_bwd(ctypes.byref(a), stream), "ring block backward")
         return dq
+
+
+    @staticmethod
+    def merge(out_acc, lse_acc, o, l):
+        """In-place LSE merge of the partial (o, l) into the fp32 accumulators (views are fine)."""
+        from flash_attention_b200 import _lib
+        from flash_attention_b200._lib import check, lib, tensor3
+
+        B, S, H, D = o.shape
+        assert out_acc.stride(3) == 1 and o.stride(3) == 1 and lse_acc.stride(2) == 1 and l.stride(2) == 1
+        dtype = _lib.FA_DTYPE_BF16 if o.dtype == torch.bfloat16 else _lib.FA_DTYPE_FP16
+        stream = ctypes.c_void_p(torch.cuda.current_stream(o.device).cuda_stream)
+        ta, tp = tensor3(out_acc), tensor3(o)
+        with torch.cuda.device(o.device):
+            check(lib().fa_merge_partial(ctypes.byref(ta), lse_acc.data_ptr(), lse_acc.stride(0), lse_acc.stride(1),
+                                         ctypes.byref(tp), l.data_ptr(), l.stride(0), l.stride(1), B, S, H, D, dtype, stream),
+                  "ring merge")
 
 
 # ------------------------------------------------------------------------------------------------
@@ -89,6 +106,31 @@ def merge_partials(out_a, lse_a, out_b, lse_b):
     wa = torch.where(torch.isnan(wa), torch.zeros_like(wa), wa).transpose(1, 2).unsqueeze(-1)
     wb = torch.where(torch.isnan(wb), torch.zeros_like(wb), wb).transpose(1, 2).unsqueeze(-1)
     return out_a * wa + out_b * wb, lse
+
+
+def _merge_into(block_ops, out_acc, lse_acc, o, l):
+    """out_acc / lse_acc (fp32, -inf = still empty; views allowed) <- merged with the partial (o, l)."""
+    fused = getattr(block_ops, "merge", None)
+    if fused is not None:
+        fused(out_acc, lse_acc, o, l)
+    else:
+        m_o, m_l = merge_partials(out_acc, lse_acc, o.float(), l)
+        out_acc.copy_(m_o)
+        lse_acc.copy_(m_l)
+
+
+def _causal_zigzag_plan(r, src, c):
+    """Pure causal mask, zigzag layout, local rows = [early chunk; late chunk] of c rows each.  What
+    the queries of rank r see of the K/V that started on rank src is one rectangular call:
+      src == r: the local sequence against itself, causally (its two chunks keep their global order);
+      src <  r: all local queries against src's early chunk, unmasked;
+      src >  r: the late local queries against both of src's chunks, unmasked.
+    Returns (q_rows, k_rows, causal) as slices of the local row axis."""
+    if src == r:
+        return slice(0, 2 * c), slice(0, 2 * c), True
+    if src < r:
+        return slice(0, 2 * c), slice(0, c), False
+    return slice(c, 2 * c), slice(0, 2 * c), False
 
 
 def _normalize_window(causal, window_size):
@@ -164,55 +206,44 @@ def zigzag_unshard(shards, dim=1):
     return torch.cat(chunks, dim=dim)
 
 
-def _split(x, chunks, dim=1):
-    out, off = [], 0
-    for _, n in chunks:
-        out.append(x.narrow(dim, off, n).contiguous())
-        off += n
-    return out
-
-
 def ring_forward(q, k, v, scale, causal, window_size, group=None, block_ops=CudaBlockOps, layout="contiguous"):
     """Forward of ring attention on this rank's shard. q: (B, S_loc, H, D); k, v: (B, S_loc, Hk, D).
     The global sequence is laid out over the ranks as `layout` says (layout_chunks).  Returns
     (out, lse) with lse fp32 (B, H, S_loc), +inf where a row sees no key."""
     p2p = _P2P(group)
     P, r = p2p.world, p2p.rank
-    S_loc = q.shape[1]
+    B, S_loc, H, D = q.shape
     window = _normalize_window(causal, window_size)
     mine = layout_chunks(layout, r, P, S_loc)
-    q_ch = _split(q, mine)
-    kv_cur = _split(k, mine) + _split(v, mine)  # [K chunks..., V chunks...]
-    n = len(mine)
-    acc = [None] * n
+    out_acc = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    lse_acc = torch.full((B, H, S_loc), float("-inf"), dtype=torch.float32, device=q.device)
+    # one rectangular call per step when the mask is purely causal on zigzag shards of one sequence per batch entry
+    fast = layout == "zigzag" and window == (-1, 0) and B == 1
+    kv_cur = [k.contiguous(), v.contiguous()]
+    offs = [sum(n for _, n in mine[:i]) for i in range(len(mine))]
     for s in range(P):
         src = (r - s) % P
-        theirs = layout_chunks(layout, src, P, S_loc)
         reqs = None
         if s + 1 < P:
             kv_nxt = [torch.empty_like(t) for t in kv_cur]
             reqs = p2p.start(kv_cur, kv_nxt)
-        for qi, (qg, qn) in enumerate(mine):
-            for ki, (kg, kn) in enumerate(theirs):
-                if not block_visible(qg, qn, kg, kn, window):
-                    continue
-                o, l = block_ops.fwd(q_ch[qi], kv_cur[ki], kv_cur[n + ki], scale, window, qg - kg)
-                if acc[qi] is None:
-                    acc[qi] = (o.float(), torch.where(torch.isinf(l), torch.full_like(l, float("-inf")), l))
-                else:
-                    acc[qi] = merge_partials(acc[qi][0], acc[qi][1], o.float(), l)
+        if fast:
+            qs, ks, cz = _causal_zigzag_plan(r, src, S_loc // 2)
+            o, l = block_ops.fwd(q[:, qs], kv_cur[0][:, ks], kv_cur[1][:, ks], scale, (-1, 0) if cz else (-1, -1), 0)
+            _merge_into(block_ops, out_acc[:, qs], lse_acc[:, :, qs], o, l)
+        else:
+            theirs = layout_chunks(layout, src, P, S_loc)
+            for qi, (qg, qn) in enumerate(mine):
+                for ki, (kg, kn) in enumerate(theirs):
+                    if not block_visible(qg, qn, kg, kn, window):
+                        continue
+                    qs, ks = slice(offs[qi], offs[qi] + qn), slice(offs[ki], offs[ki] + kn)
+                    o, l = block_ops.fwd(q[:, qs].contiguous(), kv_cur[0][:, ks].contiguous(), kv_cur[1][:, ks].contiguous(),
+                                         scale, window, qg - kg)
+                    _merge_into(block_ops, out_acc[:, qs], lse_acc[:, :, qs], o, l)
         if reqs is not None:
             p2p.finish(reqs)
             kv_cur = kv_nxt
-    outs, lses = [], []
-    for qi, (qg, qn) in enumerate(mine):
-        if acc[qi] is None:
-            outs.append(torch.zeros(q_ch[qi].shape, dtype=torch.float32, device=q.device))
-            lses.append(torch.full((q.shape[0], q.shape[2], qn), float("-inf"), device=q.device))
-        else:
-            outs.append(acc[qi][0])
-            lses.append(acc[qi][1])
-    out_acc, lse_acc = torch.cat(outs, dim=1), torch.cat(lses, dim=-1)
     lse = torch.where(torch.isinf(lse_acc) & (lse_acc < 0), torch.full_like(lse_acc, float("inf")), lse_acc)
     return out_acc.to(q.dtype), lse
 
@@ -222,29 +253,43 @@ def ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group=Non
     """Backward of ring attention.  Returns (dq, dk, dv) of this rank's shards."""
     p2p = _P2P(group)
     P, r = p2p.world, p2p.rank
-    S_loc = q.shape[1]
+    B, S_loc = q.shape[0], q.shape[1]
     window = _normalize_window(causal, window_size)
     mine = layout_chunks(layout, r, P, S_loc)
-    n = len(mine)
-    q_ch, out_ch, do_ch = _split(q, mine), _split(out, mine), _split(dout, mine)
-    lse_ch = _split(lse, mine, dim=-1)
-    kv_cur = _split(k, mine) + _split(v, mine)
-    # fp32 accumulators of dK / dV travel with their K / V chunks
+    offs = [sum(n for _, n in mine[:i]) for i in range(len(mine))]
+    fast = layout == "zigzag" and window == (-1, 0) and B == 1
+    kv_cur = [k.contiguous(), v.contiguous()]
+    # fp32 accumulators of dK / dV travel with their K / V block
     g_cur = [torch.zeros(t.shape, dtype=torch.float32, device=t.device) for t in kv_cur]
-    dq_ch = [torch.zeros(t.shape, dtype=torch.float32, device=t.device) for t in q_ch]
+    dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    dout = dout.contiguous()
     for s in range(P):
         src = (r - s) % P
-        theirs = layout_chunks(layout, src, P, S_loc)
         reqs = None
         if s + 1 < P:  # K/V of the next step can already travel; dK/dV follow after this step's compute
             kv_nxt = [torch.empty_like(t) for t in kv_cur]
             reqs = p2p.start(kv_cur, kv_nxt)
-        for qi, (qg, qn) in enumerate(mine):
-            for ki, (kg, kn) in enumerate(theirs):
-                if not block_visible(qg, qn, kg, kn, window):
-                    continue
-                dq_ch[qi] += block_ops.bwd(do_ch[qi], q_ch[qi], kv_cur[ki], kv_cur[n + ki], out_ch[qi], lse_ch[qi],
-                                           g_cur[ki], g_cur[n + ki], scale, window, qg - kg).float()
+        if fast:
+            qs, ks, cz = _causal_zigzag_plan(r, src, S_loc // 2)
+            # with one sequence per batch entry a row range of a (1, S, H, D) tensor is itself contiguous
+            dq[:, qs] += block_ops.bwd(dout[:, qs], q[:, qs], kv_cur[0][:, ks], kv_cur[1][:, ks], out[:, qs], lse[:, :, qs],
+                                       g_cur[0][:, ks], g_cur[1][:, ks], scale, (-1, 0) if cz else (-1, -1), 0).float()
+        else:
+            theirs = layout_chunks(layout, src, P, S_loc)
+            for qi, (qg, qn) in enumerate(mine):
+                for ki, (kg, kn) in enumerate(theirs):
+                    if not block_visible(qg, qn, kg, kn, window):
+                        continue
+                    qs, ks = slice(offs[qi], offs[qi] + qn), slice(offs[ki], offs[ki] + kn)
+                    whole = kn == S_loc
+                    gk = g_cur[0] if whole else g_cur[0][:, ks].contiguous()
+                    gv = g_cur[1] if whole else g_cur[1][:, ks].contiguous()
+                    dq[:, qs] += block_ops.bwd(dout[:, qs].contiguous(), q[:, qs].contiguous(), kv_cur[0][:, ks].contiguous(),
+                                               kv_cur[1][:, ks].contiguous(), out[:, qs].contiguous(),
+                                               lse[:, :, qs].contiguous(), gk, gv, scale, window, qg - kg).float()
+                    if not whole:
+                        g_cur[0][:, ks] = gk
+                        g_cur[1][:, ks] = gv
         if reqs is not None:
             p2p.finish(reqs)
         # pass the gradient accumulators of this block on (after P hops they are back home)
@@ -253,9 +298,7 @@ def ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group=Non
         g_cur = g_nxt
         if s + 1 < P:
             kv_cur = kv_nxt
-    dq = torch.cat(dq_ch, dim=1)
-    dk, dv = torch.cat(g_cur[:n], dim=1), torch.cat(g_cur[n:], dim=1)
-    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+    return dq.to(q.dtype), g_cur[0].to(k.dtype), g_cur[1].to(v.dtype)
 
 
 class RingAttnFunc(torch.autograd.Function):

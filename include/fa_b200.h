@@ -186,6 +186,16 @@ int64_t fa_bwd_workspace_bytes(int32_t batch, int32_t seqlen_q, int32_t heads, i
 int fa_combine(const float* out_parts, const float* lse_parts, void* out, float* lse, int32_t n_parts, int64_t rows,
                int32_t head_dim, int64_t out_row_stride, int32_t dtype, fa_stream_t stream);
 
+/* In-place merge of one more partial result into a running accumulator, the per-step update of
+   context-parallel ring attention (same math as the split combine above, one part at a time; the
+   reference has no multi-GPU attention and therefore no counterpart):
+     acc (batch, seqlen, heads, head_dim) fp32 and lse_acc (batch, heads, seqlen) fp32 are updated with
+     part (same shape, `dtype`) and lse_part; strides in elements, head_dim / seqlen contiguous.
+   An LSE of +inf or -inf marks a row without keys; lse_acc uses -inf for "still empty". */
+int fa_merge_partial(const FaTensor* acc, float* lse_acc, int64_t lse_acc_stride_b, int64_t lse_acc_stride_h,
+                     const FaTensor* part, const float* lse_part, int64_t lse_part_stride_b, int64_t lse_part_stride_h,
+                     int32_t batch, int32_t seqlen, int32_t heads, int32_t head_dim, int32_t dtype, fa_stream_t stream);
+
 /* sizeof() of the argument structs as compiled (0: FaTensor, 1: FaFwdArgs, 2: FaBwdArgs,
    3: FaKvcacheArgs), so that a foreign-function binding can verify its own layout. */
 int fa_abi_struct_size(int32_t which);

@@ -80,3 +80,30 @@ def test_ring_attention_two_gpus(causal, window, layout):
         for e, y in errs:
             # partial outputs are rounded to bf16 once per ring step before the merge
             assert e <= 3 * y + 2e-3, (rank, errs)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_merge_matches_torch_merge(dtype):
+    """fa_merge_partial (in place, on views) against the torch formulation used on CPU ranks."""
+    from flash_attention_b200.ring import CudaBlockOps, merge_partials
+
+    g = torch.Generator().manual_seed(3)
+    B, S, H, D = 2, 77, 3, 64
+    acc = torch.randn(B, 2 * S, H, D, generator=g).cuda()
+    lacc = torch.randn(B, H, 2 * S, generator=g).cuda()
+    o = torch.randn(B, S, H, D, generator=g).to(dtype).cuda()
+    l = torch.randn(B, H, S, generator=g).cuda()
+    lacc[0, 0, S + 1] = float("-inf")  # accumulator still empty
+    l[0, 1, 2] = float("inf")          # partial saw no key
+    lacc[1, 2, S + 5] = float("-inf")  # both empty
+    l[1, 2, 5] = float("inf")
+    want_o, want_l = merge_partials(acc[:, S:].clone(), lacc[:, :, S:].clone(), o.float(), l)
+    keep_o, keep_l = acc[:, :S].clone(), lacc[:, :, :S].clone()
+    CudaBlockOps.merge(acc[:, S:], lacc[:, :, S:], o, l)
+    torch.cuda.synchronize()
+    assert torch.allclose(acc[:, S:], want_o, atol=1e-5, rtol=1e-5)
+    assert torch.equal(torch.isinf(lacc[:, :, S:]), torch.isinf(want_l))
+    fin = ~torch.isinf(want_l)
+    assert torch.allclose(lacc[:, :, S:][fin], want_l[fin], atol=1e-5)
+    assert torch.equal(acc[:, :S], keep_o) and torch.equal(lacc[:, :, :S], keep_l)  # rows outside the view untouched
