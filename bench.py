@@ -253,6 +253,71 @@ def run_decode(args):
         dist.destroy_process_group()
 
 
+def run_rotary(args):
+    """Rotary embedding of q and k inside the default workload's packed qkv (16 x 2048 x 3 x 16 x 128 bf16 per GPU),
+    in place, forward (the backward is the same kernel with the conjugate flag).  Metric: GB/s over the bytes of
+    q and k read and written."""
+    from flash_attention_b200 import _lib
+    from flash_attention_b200.layers.rotary import apply_rotary_emb_qkv_
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    B, S, H, D = 16, 2048, 16, 128
+    g = torch.Generator(device=dev).manual_seed(5 + rank)
+    qkv = torch.randn(B, S, 3, H, D, device=dev, dtype=torch.bfloat16, generator=g)
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2, device=dev).float() / D))
+    fr = torch.outer(torch.arange(S, device=dev).float(), inv)
+    cos, sin = torch.cos(fr).bfloat16(), torch.sin(fr).bfloat16()
+    nbytes = 2.0 * 2 * B * S * H * D * 2  # q and k, read + write
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        for _ in range(max(3, args.warmup)):
+            apply_rotary_emb_qkv_(qkv, cos, sin)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with ClockSampler(local) as clk:
+            ev0.record()
+            for _ in range(args.steps):
+                apply_rotary_emb_qkv_(qkv, cos, sin)  # 268 MB of q, k per call: larger than L2
+            ev1.record()
+            barrier()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    gbs = world * nbytes / (ms * 1e-3) / 1e9
+    pk = peaks()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "rotary embedding GB/s (bf16, q and k of packed qkv, in place)", "value": gbs, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "rotary_qkv_b16_s2048_h16_d128", "batch_per_gpu": B, "seqlen": S, "heads": H, "head_dim": D,
+                       "rotary_dim": D, "style": "neox", "l2": "268 MB of q and k per call, larger than L2",
+                       "bytes_model": "2 (q, k) x 2 (read, write) x B S H D x 2 B"},
+            "roofline": {"bound": "hbm", "kernel": "rotary_vec_kernel", "achieved": gbs / world, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / world / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"]},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": args.steps, "clocks": clk.summary(),
+            "device_status": _lib.lib().fa_device_status(),
+        }))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -266,6 +331,8 @@ def main():
         from flash_attention_b200 import ring_bench
 
         return ring_bench.main(args)
+    if args.workload == "rotary":
+        return run_rotary(args)
     if args.workload == "decode":
         return run_decode(args)
     wl = args.workload

@@ -88,10 +88,25 @@ class FaKvcacheArgs(C.Structure):
     ]
 
 
+class FaRotaryArgs(C.Structure):
+    _fields_ = [
+        ("x", FaTensor), ("out", FaTensor),
+        ("cos", c_vp), ("sin", c_vp),
+        ("seqlen_offsets", c_vp), ("cu_seqlens", c_vp),
+        ("batch", c_i32), ("seqlen", c_i32), ("heads", c_i32), ("head_dim", c_i32),
+        ("total", c_i32),
+        ("rotary_dim", c_i32), ("seqlen_ro", c_i32),
+        ("seqlen_offset", c_i32),
+        ("dtype", c_i32),
+        ("interleaved", c_i32),
+        ("conjugate", c_i32),
+    ]
+
+
 EXPORTS = (
     "fa_fwd", "fa_bwd", "fa_fwd_kvcache", "fa_fwd_num_splits", "fa_kvcache_plan", "fa_bwd_workspace_bytes",
     "fa_combine", "fa_last_error", "fa_build_info", "fa_device_status", "fa_abi_struct_size",
-    "fa_fwd_kvcache_noalloc", "fa_noalloc_scratch_bytes", "fa_merge_partial",
+    "fa_fwd_kvcache_noalloc", "fa_noalloc_scratch_bytes", "fa_merge_partial", "fa_rotary",
 )
 
 _lib = None
@@ -127,12 +142,14 @@ def lib():
         L.fa_merge_partial.argtypes = [C.POINTER(FaTensor), c_vp, c_i64, c_i64, C.POINTER(FaTensor), c_vp, c_i64, c_i64,
                                        c_i32, c_i32, c_i32, c_i32, c_i32, c_vp]
         L.fa_merge_partial.restype = C.c_int
+        L.fa_rotary.argtypes = [C.POINTER(FaRotaryArgs), c_vp]
+        L.fa_rotary.restype = C.c_int
         L.fa_last_error.restype = C.c_char_p
         L.fa_build_info.restype = C.c_char_p
         L.fa_device_status.restype = C.c_int
         L.fa_abi_struct_size.argtypes = [c_i32]
         L.fa_abi_struct_size.restype = C.c_int
-        for which, st in enumerate((FaTensor, FaFwdArgs, FaBwdArgs, FaKvcacheArgs)):
+        for which, st in enumerate((FaTensor, FaFwdArgs, FaBwdArgs, FaKvcacheArgs, FaRotaryArgs)):
             if L.fa_abi_struct_size(which) != C.sizeof(st):
                 raise ImportError("libfa_b200.so and flash_attention_b200/_lib.py disagree on the layout of %s" % st.__name__)
         _lib = L

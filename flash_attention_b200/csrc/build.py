@@ -20,6 +20,7 @@ SOURCES = [
     "generic_bwd.cu",
     "combine.cu",
     "kvcache_prep.cu",
+    "rotary.cu",
     "sm100/fwd_tc.cu",
     "sm100/bwd_tc.cu",
     "sm100/bwd_dq_tc.cu",

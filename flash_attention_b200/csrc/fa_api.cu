@@ -15,6 +15,7 @@ int bwd_pre(const FaBwdArgs& a, int zero_dq, cudaStream_t st);
 int bwd_post(const FaBwdArgs& a, cudaStream_t st);
 int bwd_post_blocked(const FaBwdArgs& a, int dhp, cudaStream_t st);
 int bwd_generic_main(const FaBwdArgs& a, cudaStream_t st);
+int rotary(const FaRotaryArgs& a, cudaStream_t st);
 int merge_partial(const FaTensor& acc, float* lse_acc, int64_t lacc_sb, int64_t lacc_sh, const FaTensor& part,
                   const float* lse_part, int64_t lpart_sb, int64_t lpart_sh, int B, int S, int H, int D, int dtype,
                   cudaStream_t st);
@@ -99,7 +100,7 @@ const char* fa_last_error(void) { return fa_host::g_err; }
 
 const char* fa_build_info(void) {
   return "libfa_b200 arch=sm_100a kernels=fwd_tc(tcgen05+TMA),bwd_dkdv_tc(tcgen05+TMA),bwd_dq_tc(tcgen05+TMA),decode_splitkv(TMA),"
-         "fwd_generic(mma.sync),bwd_generic(mma.sync),combine,merge_partial,bwd_dot_do_o,bwd_convert_dq,kvcache_prep";
+         "fwd_generic(mma.sync),bwd_generic(mma.sync),combine,merge_partial,rotary,bwd_dot_do_o,bwd_convert_dq,kvcache_prep";
 }
 
 int fa_device_status(void) {
@@ -116,6 +117,7 @@ int fa_abi_struct_size(int32_t which) {
     case 1: return (int)sizeof(FaFwdArgs);
     case 2: return (int)sizeof(FaBwdArgs);
     case 3: return (int)sizeof(FaKvcacheArgs);
+    case 4: return (int)sizeof(FaRotaryArgs);
     default: return -1;
   }
 }
@@ -364,6 +366,23 @@ int fa_merge_partial(const FaTensor* acc, float* lse_acc, int64_t lse_acc_stride
              "accumulator rows must be 16-byte aligned, partial rows 8-byte aligned");
   return fa::merge_partial(*acc, lse_acc, lse_acc_stride_b, lse_acc_stride_h, *part, lse_part, lse_part_stride_b,
                            lse_part_stride_h, batch, seqlen, heads, head_dim, dtype, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int fa_rotary(const FaRotaryArgs* a, fa_stream_t stream) {
+  FA_REQUIRE(a != nullptr, "null arguments");
+  FA_REQUIRE(a->dtype == FA_DTYPE_FP16 || a->dtype == FA_DTYPE_BF16, "rotary only supports fp16 and bf16 data type");
+  FA_REQUIRE(a->batch >= 0 && a->seqlen >= 0 && a->heads > 0 && a->head_dim > 0, "bad sizes");
+  FA_REQUIRE(a->head_dim <= 256, "Only support headdim <= 256");
+  FA_REQUIRE(a->rotary_dim >= 0 && a->rotary_dim % 2 == 0, "rotary_dim must be even");
+  FA_REQUIRE(a->rotary_dim <= a->head_dim, "rotary_dim must be <= headdim");
+  FA_REQUIRE(a->cu_seqlens != nullptr || a->seqlen_ro >= a->seqlen, "seqlen_ro must be >= seqlen");
+  FA_REQUIRE(a->seqlen_offsets != nullptr || a->cu_seqlens != nullptr || a->seqlen_offset + a->seqlen <= a->seqlen_ro,
+             "seqlen_offsets + seqlen must be <= seqlen_ro");
+  const int64_t rows = a->cu_seqlens ? (int64_t)a->total : (int64_t)a->batch * a->seqlen;
+  if (rows == 0) return 0;
+  FA_REQUIRE(a->x.ptr && a->out.ptr, "x / out: null pointer");
+  FA_REQUIRE(a->rotary_dim == 0 || (a->cos && a->sin), "cos / sin: null pointer");
+  return fa::rotary(*a, reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

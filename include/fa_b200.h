@@ -196,8 +196,31 @@ int fa_merge_partial(const FaTensor* acc, float* lse_acc, int64_t lse_acc_stride
                      const FaTensor* part, const float* lse_part, int64_t lse_part_stride_b, int64_t lse_part_stride_h,
                      int32_t batch, int32_t seqlen, int32_t heads, int32_t head_dim, int32_t dtype, fa_stream_t stream);
 
+/* Rotary position embedding, the step before attention.  Replaces apply_rotary
+   (flash_attn/ops/triton/rotary.py:143-240, kernel :17-140) behind apply_rotary_emb,
+   apply_rotary_emb_qkv_ and apply_rotary_emb_kv_ (flash_attn/layers/rotary.py:35-330).
+   x and out are (batch, seqlen, heads, head_dim), or packed (total, heads, head_dim) with
+   cu_seqlens (stride_b unused); out may be x.  cos / sin are (seqlen_ro, rotary_dim / 2) tables of
+   the same 16-bit type as x, contiguous.  Row s of sequence b uses table row
+   s + seqlen_offsets[b] (or + seqlen_offset); rows past the tables are left unrotated. */
+typedef struct FaRotaryArgs {
+  FaTensor x, out;
+  const void* cos;
+  const void* sin;
+  const int32_t* seqlen_offsets; /* (batch) or NULL */
+  const int32_t* cu_seqlens;     /* (batch + 1) or NULL */
+  int32_t batch, seqlen, heads, head_dim; /* seqlen: max_seqlen for packed input */
+  int32_t total;                 /* rows of a packed input */
+  int32_t rotary_dim, seqlen_ro;
+  int32_t seqlen_offset;
+  int32_t dtype;
+  int32_t interleaved;           /* pairs (2i, 2i+1) instead of (i, i + rotary_dim/2) */
+  int32_t conjugate;             /* rotate by the negative angle: the backward */
+} FaRotaryArgs;
+int fa_rotary(const FaRotaryArgs* args, fa_stream_t stream);
+
 /* sizeof() of the argument structs as compiled (0: FaTensor, 1: FaFwdArgs, 2: FaBwdArgs,
-   3: FaKvcacheArgs), so that a foreign-function binding can verify its own layout. */
+   3: FaKvcacheArgs, 4: FaRotaryArgs), so that a foreign-function binding can verify its own layout. */
 int fa_abi_struct_size(int32_t which);
 
 /* Message for the last non-zero status returned on this thread. */

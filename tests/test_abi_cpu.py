@@ -36,7 +36,7 @@ def test_every_declared_symbol_is_exported(lib):
 def test_struct_layouts_match(lib):
     from flash_attention_b200 import _lib
 
-    for which, st in enumerate((_lib.FaTensor, _lib.FaFwdArgs, _lib.FaBwdArgs, _lib.FaKvcacheArgs)):
+    for which, st in enumerate((_lib.FaTensor, _lib.FaFwdArgs, _lib.FaBwdArgs, _lib.FaKvcacheArgs, _lib.FaRotaryArgs)):
         assert lib.fa_abi_struct_size(which) == ctypes.sizeof(st)
     assert lib.fa_abi_struct_size(99) == -1
     assert b"sm_100a" in lib.fa_build_info()
@@ -63,6 +63,32 @@ def test_argument_validation_happens_before_launch(lib):
     k.num_splits = 200
     assert lib.fa_kvcache_plan(ctypes.byref(k), 148, None, None) < 0
     assert b"num_splits" in lib.fa_last_error()
+
+
+def test_rotary_and_merge_validate_before_launch(lib):
+    from flash_attention_b200 import _lib
+
+    r = _lib.FaRotaryArgs()
+    r.batch, r.seqlen, r.heads, r.head_dim, r.rotary_dim, r.seqlen_ro, r.dtype = 1, 8, 2, 64, 96, 8, 1
+    assert lib.fa_rotary(ctypes.byref(r), None) != 0
+    assert b"rotary_dim must be <= headdim" in lib.fa_last_error()
+    r.rotary_dim, r.seqlen_ro = 32, 4
+    assert lib.fa_rotary(ctypes.byref(r), None) != 0
+    assert b"seqlen_ro must be >= seqlen" in lib.fa_last_error()
+    r.seqlen_ro, r.head_dim = 8, 300
+    assert lib.fa_rotary(ctypes.byref(r), None) != 0
+    assert b"headdim <= 256" in lib.fa_last_error()
+    r.head_dim, r.dtype = 64, 7
+    assert lib.fa_rotary(ctypes.byref(r), None) != 0
+    assert b"fp16 and bf16" in lib.fa_last_error()
+    r.dtype = 0
+    assert lib.fa_rotary(ctypes.byref(r), None) != 0  # null x
+    assert b"null" in lib.fa_last_error()
+    r.seqlen = 0
+    assert lib.fa_rotary(ctypes.byref(r), None) == 0  # nothing to do
+    t = _lib.FaTensor(None, 0, 0, 0)
+    assert lib.fa_merge_partial(ctypes.byref(t), None, 0, 0, ctypes.byref(t), None, 0, 0, 1, 1, 1, 64, 1, None) != 0
+    assert b"null" in lib.fa_last_error()
 
 
 def test_split_heuristic_matches_reference_rules(lib):
