@@ -97,3 +97,60 @@ def test_kvcache_int_cache_seqlens_and_no_seqlens():
     ref, _ = O.attention_oracle(q, kc, vc)
     low, _ = O.attention_oracle(q, kc, vc, upcast=False, reorder_ops=True)
     assert_within(out, ref, low, mult=3)
+
+
+def test_decode_loop_in_a_cuda_graph():
+    """The decode step (append one token with rotary + attend) captured once in a CUDA graph and
+    replayed for several tokens, as the generation loop of the reference does
+    (flash_attn/utils/generation.py:662-700): every replay must give what eager calls give, and the
+    cache must end up identical.  The lengths live on the device and advance between replays."""
+    import flash_attention_b200 as fa
+
+    g = torch.Generator().manual_seed(11)
+    B, cap, H, Hk, D, steps = 4, 512, 8, 2, 128, 6
+    dev = "cuda"
+    kc0 = torch.randn(B, cap, Hk, D, generator=g).bfloat16().to(dev)
+    vc0 = torch.randn(B, cap, Hk, D, generator=g).bfloat16().to(dev)
+    lens0 = torch.tensor([17, 130, 255, 300], dtype=torch.int32, device=dev)
+    qs = torch.randn(steps, B, 1, H, D, generator=g).bfloat16().to(dev)
+    kn = torch.randn(steps, B, 1, Hk, D, generator=g).bfloat16().to(dev)
+    vn = torch.randn(steps, B, 1, Hk, D, generator=g).bfloat16().to(dev)
+    inv = 1.0 / (10000 ** (torch.arange(0, D, 2, device=dev).float() / D))
+    fr = torch.outer(torch.arange(cap, device=dev).float(), inv)
+    cos, sin = torch.cos(fr).bfloat16(), torch.sin(fr).bfloat16()
+
+    def eager():
+        kc, vc, lens = kc0.clone(), vc0.clone(), lens0.clone()
+        outs = []
+        for t in range(steps):
+            outs.append(fa.flash_attn_with_kvcache(qs[t], kc, vc, kn[t], vn[t], cos, sin, lens, causal=True,
+                                                   rotary_interleaved=False).clone())
+            lens += 1
+        return outs, kc, vc
+
+    want, kc_want, vc_want = eager()
+    kc, vc, lens = kc0.clone(), vc0.clone(), lens0.clone()
+    q_in, k_in, v_in = qs[0].clone(), kn[0].clone(), vn[0].clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):  # warm-up on the capture stream, then restore the state it changed
+        fa.flash_attn_with_kvcache(q_in, kc, vc, k_in, v_in, cos, sin, lens, causal=True, rotary_interleaved=False)
+    torch.cuda.current_stream().wait_stream(side)
+    kc.copy_(kc0)
+    vc.copy_(vc0)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out_g = fa.flash_attn_with_kvcache(q_in, kc, vc, k_in, v_in, cos, sin, lens, causal=True, rotary_interleaved=False)
+        lens += 1
+    kc.copy_(kc0)
+    vc.copy_(vc0)
+    lens.copy_(lens0)
+    for t in range(steps):
+        q_in.copy_(qs[t])
+        k_in.copy_(kn[t])
+        v_in.copy_(vn[t])
+        graph.replay()
+        assert torch.equal(out_g, want[t]), t
+    torch.cuda.synchronize()
+    assert torch.equal(kc, kc_want) and torch.equal(vc, vc_want)
+    assert torch.equal(lens, lens0 + steps)
