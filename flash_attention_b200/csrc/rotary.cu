@@ -177,7 +177,7 @@ static int rotary_t(const FaRotaryArgs& a, cudaStream_t st) {
     const int64_t items = rows * (p.n_rot + p.n_tail);
     if (items == 0) return 0;
     const int64_t want = (items + 255) / 256;
-    const unsigned grid = (unsigned)(want < (int64_t)sms * 16 ? want : (int64_t)sms * 16);
+    const unsigned grid = (unsigned)(want < (int64_t)sms * 8 ? want : (int64_t)sms * 8);  // one resident wave, grid-stride
     if (a.interleaved)
       rotary_vec_kernel<T, true><<<grid, 256, 0, st>>>(p);
     else
@@ -188,7 +188,7 @@ static int rotary_t(const FaRotaryArgs& a, cudaStream_t st) {
   const int64_t items = rows * (half + (inplace ? 0 : a.head_dim - a.rotary_dim));
   if (items == 0) return 0;
   const int64_t want = (items + 255) / 256;
-  const unsigned grid = (unsigned)(want < (int64_t)sms * 16 ? want : (int64_t)sms * 16);
+  const unsigned grid = (unsigned)(want < (int64_t)sms * 8 ? want : (int64_t)sms * 8);  // one resident wave, grid-stride
   rotary_scalar_kernel<T><<<grid, 256, 0, st>>>(p);
   return fa_host::check_launch("rotary_scalar_kernel");
 }

@@ -1,7 +1,8 @@
-// Forward attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), head dim <= 128.
+// Forward attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), head dim <= 256.
 //
 // One CTA owns 256 query rows of one (batch, head): two 128-row tiles that take turns on the
-// tensor pipe.  Warp roles (384 threads):
+// tensor pipe (head dims above 128: one tile, because O alone fills 256 TMEM columns; warps 4-7 idle).
+// Warp roles (384 threads):
 //   warps 0-3   softmax of tile 0  (one thread per query row; tcgen05.ld 32x32b gives a thread its row)
 //   warps 4-7   softmax of tile 1
 //   warp  8     TMA producer: Q tiles once, then K(j), V(j), K(j+1), ... through a ring of slots
@@ -40,8 +41,11 @@ template <int DH>
 struct Cfg {
   static constexpr int NCHUNK = DH / 64;
   static constexpr int TILE_BYTES = NCHUNK * kChunkBytes;
-  static constexpr int STAGES = DH == 128 ? 4 : 8;
-  static constexpr int SMEM_TILES = (2 + STAGES) * TILE_BYTES;
+  // Head dims up to 128: two 128-row query tiles per CTA ping-pong on the tensor pipe.  Up to 256: O alone
+  // needs 256 TMEM columns and a tile is 64 KiB, so one query tile per CTA and a 2-slot (K, V) ring.
+  static constexpr int NT = DH > 128 ? 1 : 2;
+  static constexpr int STAGES = DH > 128 ? 2 : (DH == 128 ? 4 : 8);
+  static constexpr int SMEM_TILES = (NT + STAGES) * TILE_BYTES;
   static constexpr int NBAR = 2 + 2 * STAGES + 6;
   static constexpr int SMEM_BYTES = SMEM_TILES + NBAR * 8 + 16 + 1024;  // + barriers, tmem ptr/abort, align slack
   static constexpr int TMEM_COLS = 512;
@@ -72,8 +76,8 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   const uint32_t s_base = smem_addr(smem);
-  const uint32_t sQ = s_base;                        // 2 tiles
-  const uint32_t sKV = s_base + 2 * C::TILE_BYTES;   // STAGES slots
+  const uint32_t sQ = s_base;                          // NT tiles
+  const uint32_t sKV = s_base + C::NT * C::TILE_BYTES;  // STAGES slots
   const uint32_t bar0 = s_base + C::SMEM_TILES;
   auto bar_qfull = [&](int t) { return bar0 + 8 * t; };
   auto bar_full = [&](int s) { return bar0 + 8 * (2 + s); };
@@ -90,7 +94,7 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
                               a.use_mask_shift, a.mask_shift, b);
   // heaviest blocks (largest row index under a causal mask) first
   const int mblk = (int)gridDim.x - 1 - (int)blockIdx.x;
-  const int m_base = mblk * 2 * kBM;
+  const int m_base = mblk * C::NT * kBM;
   if (m_base >= si.sq) return;  // uniform for the CTA
 
   // per-tile key block ranges
@@ -99,7 +103,7 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const int m0 = m_base + t * kBM;
-    active[t] = m0 < si.sq;
+    active[t] = t < C::NT && m0 < si.sq;
     if (active[t]) {
       key_block_range(m0, kBM, kBN, si.sk, si.shift, a.window_left, a.window_right, lo[t], hi[t]);
     } else {
@@ -334,7 +338,7 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
         const uint32_t d_lo = (uint32_t)d_base, d_hi = (uint32_t)(d_base >> 32);
         auto dsc = [&](uint32_t lo_add) { return ((uint64_t)d_hi << 32) | (uint64_t)(d_lo + lo_add); };
         constexpr uint32_t kMn = (uint32_t)((kChunkBytes - 16) >> 4) << 16;  // K-major -> MN-major (LBO = chunk stride)
-        constexpr uint32_t kTile16 = C::TILE_BYTES >> 4, oKV = (2 * C::TILE_BYTES) >> 4;
+        constexpr uint32_t kTile16 = C::TILE_BYTES >> 4, oKV = (C::NT * C::TILE_BYTES) >> 4;
         auto issue_s = [&](int t, int slot) {
           const uint32_t d = tmem + (t ? C::COL_S1 : C::COL_S0);
           const uint32_t a_lo = t ? kTile16 : 0u, b_lo = oKV + slot * kTile16;
@@ -449,7 +453,7 @@ int launch_fwd_tc(const FaFwdArgs& a, cudaStream_t st) {
     }
     attr_set = true;
   }
-  dim3 grid((a.seqlen_q + 2 * kBM - 1) / (2 * kBM), a.heads, a.batch);
+  dim3 grid((a.seqlen_q + C::NT * kBM - 1) / (C::NT * kBM), a.heads, a.batch);
   kern<<<grid, 384, C::SMEM_BYTES, st>>>(P);
   return fa_host::check_launch("fwd_tc_kernel");
 }
@@ -457,7 +461,7 @@ int launch_fwd_tc(const FaFwdArgs& a, cudaStream_t st) {
 }  // namespace
 
 bool fwd_tc_eligible(const FaFwdArgs& a) {
-  if (a.head_dim > 128 || a.p_dropout > 0.f || a.s_dmask || a.num_splits > 1) return false;
+  if (a.head_dim > 256 || a.p_dropout > 0.f || a.s_dmask || a.num_splits > 1) return false;
   if (a.seqused_k || a.kv_batch_idx) return false;
   if (a.seqlen_k <= 0) return false;
   if (!tma_compatible(a.q) || !tma_compatible(a.k) || !tma_compatible(a.v)) return false;
@@ -470,7 +474,8 @@ bool fwd_tc_eligible(const FaFwdArgs& a) {
 int fwd_tc(const FaFwdArgs& a, cudaStream_t st) {
   const bool bf = a.dtype == FA_DTYPE_BF16;
   if (a.head_dim <= 64) return bf ? launch_fwd_tc<__nv_bfloat16, 64>(a, st) : launch_fwd_tc<__half, 64>(a, st);
-  return bf ? launch_fwd_tc<__nv_bfloat16, 128>(a, st) : launch_fwd_tc<__half, 128>(a, st);
+  if (a.head_dim <= 128) return bf ? launch_fwd_tc<__nv_bfloat16, 128>(a, st) : launch_fwd_tc<__half, 128>(a, st);
+  return bf ? launch_fwd_tc<__nv_bfloat16, 256>(a, st) : launch_fwd_tc<__half, 256>(a, st);
 }
 
 int fwd_tc_status(bool clear) {

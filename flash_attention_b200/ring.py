@@ -168,10 +168,35 @@ class _P2P:
             ops.append(dist.P2POp(dist.irecv, r, self.prev, group=self.group))
         return dist.batch_isend_irecv(ops)
 
+    def start_to(self, send_tensors, recv_tensors, hops):
+        """Send to the rank `hops` places back in the ring, receive from the rank `hops` places ahead."""
+        dst, src = (self.rank - hops) % self.world, (self.rank + hops) % self.world
+        if self.group is not None:
+            dst, src = dist.get_global_rank(self.group, dst), dist.get_global_rank(self.group, src)
+        ops = []
+        for s, r in zip(send_tensors, recv_tensors):
+            ops.append(dist.P2POp(dist.isend, s, dst, group=self.group))
+            ops.append(dist.P2POp(dist.irecv, r, src, group=self.group))
+        return dist.batch_isend_irecv(ops)
+
     @staticmethod
     def finish(reqs):
         for r in reqs:
             r.wait()
+
+
+def ring_steps(layout, world, s_loc, window):
+    """Number of ring steps after which no rank can see any key of the block it would receive next
+    (the same on every rank).  P for full or causal attention; fewer under a sliding window, e.g. 2 for
+    contiguous shards of 4096 rows and window (4096, 0)."""
+    last = 0
+    for s in range(1, world):
+        for r in range(world):
+            mine, theirs = layout_chunks(layout, r, world, s_loc), layout_chunks(layout, (r - s) % world, world, s_loc)
+            if any(block_visible(qg, qn, kg, kn, window) for qg, qn in mine for kg, kn in theirs):
+                last = s
+                break
+    return last + 1
 
 
 def layout_chunks(layout, rank, world, s_loc):
@@ -221,10 +246,11 @@ def ring_forward(q, k, v, scale, causal, window_size, group=None, block_ops=Cuda
     fast = layout == "zigzag" and window == (-1, 0) and B == 1
     kv_cur = [k.contiguous(), v.contiguous()]
     offs = [sum(n for _, n in mine[:i]) for i in range(len(mine))]
-    for s in range(P):
+    n_steps = ring_steps(layout, P, S_loc, window)
+    for s in range(n_steps):
         src = (r - s) % P
         reqs = None
-        if s + 1 < P:
+        if s + 1 < n_steps:
             kv_nxt = [torch.empty_like(t) for t in kv_cur]
             reqs = p2p.start(kv_cur, kv_nxt)
         if fast:
@@ -263,10 +289,11 @@ def ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group=Non
     g_cur = [torch.zeros(t.shape, dtype=torch.float32, device=t.device) for t in kv_cur]
     dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
     dout = dout.contiguous()
-    for s in range(P):
+    n_steps = ring_steps(layout, P, S_loc, window)
+    for s in range(n_steps):
         src = (r - s) % P
         reqs = None
-        if s + 1 < P:  # K/V of the next step can already travel; dK/dV follow after this step's compute
+        if s + 1 < n_steps:  # K/V of the next step can already travel; dK/dV follow after this step's compute
             kv_nxt = [torch.empty_like(t) for t in kv_cur]
             reqs = p2p.start(kv_cur, kv_nxt)
         if fast:
@@ -292,12 +319,19 @@ def ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group=Non
                         g_cur[1][:, ks] = gv
         if reqs is not None:
             p2p.finish(reqs)
-        # pass the gradient accumulators of this block on (after P hops they are back home)
-        g_nxt = [torch.empty_like(t) for t in g_cur]
-        p2p.finish(p2p.start(g_cur, g_nxt))
-        g_cur = g_nxt
-        if s + 1 < P:
+        if s + 1 < n_steps:
+            # pass the gradient accumulators of this block on together with its K / V
+            g_nxt = [torch.empty_like(t) for t in g_cur]
+            p2p.finish(p2p.start(g_cur, g_nxt))
+            g_cur = g_nxt
             kv_cur = kv_nxt
+    # the accumulators now held belong to the block that started n_steps - 1 ranks back: send them home
+    # (for a full ring that rank is the next one; a direct transfer when a window ended the ring early)
+    hops_home = (n_steps - 1) % P
+    if hops_home:
+        g_nxt = [torch.empty_like(t) for t in g_cur]
+        p2p.finish(p2p.start_to(g_cur, g_nxt, hops_home))
+        g_cur = g_nxt
     return dq.to(q.dtype), g_cur[0].to(k.dtype), g_cur[1].to(v.dtype)
 
 
