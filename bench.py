@@ -41,6 +41,9 @@ WORKLOADS = {
     "train_b16_s2048_h16_d128": (16, 2048, 16, 16, 128, False, torch.bfloat16),
     "train_b16_s2048_h32_d64_causal": (16, 2048, 32, 32, 64, True, torch.bfloat16),
     "gqa_b1_s32768_h32_hk8_d128_causal": (1, 32768, 32, 8, 128, True, torch.bfloat16),
+    "train_b16_s2048_h32_d64": (16, 2048, 32, 32, 64, False, torch.bfloat16),
+    "train_b16_s2048_h8_d256_causal": (16, 2048, 8, 8, 256, True, torch.bfloat16),
+    "train_b16_s2048_h8_d256": (16, 2048, 8, 8, 256, False, torch.bfloat16),
 }
 DEFAULT = "train_b16_s2048_h16_d128_causal"
 
