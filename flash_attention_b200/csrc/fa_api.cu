@@ -13,7 +13,6 @@ namespace fa {
 int fwd_generic(const FaFwdArgs& a, cudaStream_t st);
 int bwd_pre(const FaBwdArgs& a, int zero_dq, cudaStream_t st);
 int bwd_post(const FaBwdArgs& a, cudaStream_t st);
-int bwd_post_blocked(const FaBwdArgs& a, int dhp, cudaStream_t st);
 int bwd_generic_main(const FaBwdArgs& a, cudaStream_t st);
 int rotary(const FaRotaryArgs& a, cudaStream_t st);
 int merge_partial(const FaTensor& acc, float* lse_acc, int64_t lacc_sb, int64_t lacc_sh, const FaTensor& part,
@@ -158,14 +157,10 @@ int fa_fwd_num_splits(int32_t batch, int32_t heads, int32_t seqlen_q, int32_t se
 
 int64_t fa_bwd_workspace_bytes(int32_t batch, int32_t seqlen_q, int32_t heads, int32_t head_dim, int32_t total_q,
                                int32_t is_varlen) {
-  // the larger of the two layouts the kernels may use: plain rows (any-shape kernel) and 128-row
-  // blocks of the padded head dim (tensor-core kernel, fa_common.cuh: dq_blocked_offset)
+  // fp32 rows in the layout of dq, used by the any-shape kernel only (the tensor-core kernels
+  // write dq directly and leave the workspace untouched)
   int64_t rows = is_varlen ? (int64_t)total_q : (int64_t)batch * seqlen_q;
-  int64_t plain = rows * heads * head_dim * (int64_t)sizeof(float);
-  int64_t dhp = head_dim <= 64 ? 64 : (head_dim <= 128 ? 128 : head_dim);
-  int64_t units = is_varlen ? (int64_t)heads : (int64_t)batch * heads;
-  int64_t blocked = units * fa::dq_blocks_per_unit(is_varlen != 0, seqlen_q, total_q, batch) * 128 * dhp * (int64_t)sizeof(float);
-  return plain > blocked ? plain : blocked;
+  return rows * heads * head_dim * (int64_t)sizeof(float);
 }
 
 int fa_fwd(const FaFwdArgs* a, fa_stream_t stream) {

@@ -97,25 +97,6 @@ __device__ __forceinline__ void query_block_range(int n0, int BN, int BM, int sq
   if (hi < lo) hi = lo;
 }
 
-// Blocked layout of the fp32 dQ accumulator used by the tensor-core backward: the accumulator is a
-// sequence of 128-row blocks per (batch, head) [packed input: per head, sequence b starting at block
-// q_row0/128 + b so that sequences never share a block]; a block is stored as
-//   [half w of the head dim][32-row quarter][4-column chunk][row in quarter][4 floats]
-// which is the order in which one warp drains its piece of dQ from TMEM, so that a block piece is
-// one contiguous run of bytes for a bulk reduction.  DHP = padded head dim (64 or 128).
-__host__ __device__ __forceinline__ int64_t dq_block_index(bool varlen, int b, int h, int heads, int q_row0,
-                                                           int blocks_per_unit) {
-  return varlen ? (int64_t)h * blocks_per_unit + (q_row0 / 128 + b) : ((int64_t)b * heads + h) * blocks_per_unit;
-}
-__host__ __device__ __forceinline__ int64_t dq_blocked_offset(int64_t block, int row, int col, int DHP) {
-  const int half = DHP / 2;
-  const int w = col / half, dd = col % half;
-  return ((block * 2 + w) * 4 + (row >> 5)) * (int64_t)(32 * half) + ((dd >> 2) * 32 + (row & 31)) * 4 + (dd & 3);
-}
-__host__ __device__ __forceinline__ int dq_blocks_per_unit(bool varlen, int seqlen_q, int total_q, int batch) {
-  return varlen ? total_q / 128 + batch + 1 : (seqlen_q + 127) / 128;
-}
-
 template <typename T>
 struct Pack;
 template <>

@@ -94,34 +94,6 @@ __global__ void __launch_bounds__(128) bwd_convert_dq_kernel(const __grid_consta
   }
 }
 
-// dQ = cast(dq_accum * softmax_scale) from the BLOCKED accumulator of the tensor-core backward
-// (layout: dq_blocked_offset in fa_common.cuh).  One thread per query row of a 128-row block, so
-// that a warp's loads of one 4-column chunk are 512 contiguous bytes.  grid (blocks, heads, batch).
-template <typename T>
-__global__ void __launch_bounds__(128) bwd_convert_dq_blocked_kernel(const __grid_constant__ FaBwdArgs p, const int dhp,
-                                                                     const int blocks_per_unit) {
-  const int r = threadIdx.x, mblk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const SeqInfo si = seq_info(p.cu_seqlens_q, p.cu_seqlens_k, nullptr, nullptr, p.seqlen_q, p.seqlen_k,
-                              p.use_mask_shift, p.mask_shift, b);
-  const int row = mblk * 128 + r;
-  if (row >= si.sq) return;
-  const int64_t blk = dq_block_index(p.cu_seqlens_q != nullptr, b, h, p.heads, (int)si.q_row0, blocks_per_unit) + mblk;
-  T* dq = reinterpret_cast<T*>(p.dq.ptr) + si.q_batch * p.dq.stride_b + (si.q_row0 + row) * p.dq.stride_s +
-          (int64_t)h * p.dq.stride_h;
-  const float sc = p.softmax_scale;
-  for (int c = 0; c < p.head_dim; c += 8) {
-    const float4 x = *reinterpret_cast<const float4*>(p.dq_accum + dq_blocked_offset(blk, r, c, dhp));
-    const float4 y = *reinterpret_cast<const float4*>(p.dq_accum + dq_blocked_offset(blk, r, c + 4, dhp));
-    uint4 o;
-    o.x = Pack<T>::two(x.x * sc, x.y * sc);
-    o.y = Pack<T>::two(x.z * sc, x.w * sc);
-    o.z = Pack<T>::two(y.x * sc, y.y * sc);
-    o.w = Pack<T>::two(y.z * sc, y.w * sc);
-    *reinterpret_cast<uint4*>(dq + c) = o;
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
 template <typename T, int DP>
 __device__ __forceinline__ void load_tile_64b(T* s, const T* g, int64_t row_stride, int row0, int nrows_valid, int D,
                                               int tid) {
@@ -390,15 +362,6 @@ int bwd_post_t(const FaBwdArgs& a, cudaStream_t st) {
 
 int bwd_pre(const FaBwdArgs& a, int zero_dq, cudaStream_t st) {
   return a.dtype == FA_DTYPE_BF16 ? bwd_pre_t<__nv_bfloat16>(a, zero_dq, st) : bwd_pre_t<__half>(a, zero_dq, st);
-}
-int bwd_post_blocked(const FaBwdArgs& a, int dhp, cudaStream_t st) {
-  const int bpu = dq_blocks_per_unit(a.cu_seqlens_q != nullptr, a.seqlen_q, a.total_q, a.batch);
-  dim3 grid((a.seqlen_q + 127) / 128, a.heads, a.batch);
-  if (a.dtype == FA_DTYPE_BF16)
-    bwd_convert_dq_blocked_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(a, dhp, bpu);
-  else
-    bwd_convert_dq_blocked_kernel<__half><<<grid, 128, 0, st>>>(a, dhp, bpu);
-  return fa_host::check_launch("bwd_convert_dq_blocked_kernel");
 }
 int bwd_post(const FaBwdArgs& a, cudaStream_t st) {
   return a.dtype == FA_DTYPE_BF16 ? bwd_post_t<__nv_bfloat16>(a, st) : bwd_post_t<__half>(a, st);

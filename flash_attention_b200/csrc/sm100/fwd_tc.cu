@@ -55,7 +55,6 @@ struct Cfg {
 struct FwdTcParams {
   CUtensorMap tq, tk, tv;
   FaFwdArgs a;
-  int debug;  // timing experiments only (FA_B200_DEBUG_FWD); 0 in normal use
 };
 
 template <typename T>
@@ -433,10 +432,6 @@ int launch_fwd_tc(const FaFwdArgs& a, cudaStream_t st) {
   using C = Cfg<DH>;
   FwdTcParams P;
   P.a = a;
-  {
-    const char* dbg = getenv("FA_B200_DEBUG_FWD");
-    P.debug = dbg ? atoi(dbg) : 0;
-  }
   const bool varlen = a.cu_seqlens_q != nullptr;
   const int64_t q_rows = varlen ? a.total_q : a.seqlen_q, k_rows = varlen ? a.total_k : a.seqlen_k;
   const int64_t nb = varlen ? 1 : a.batch;
