@@ -24,6 +24,7 @@ SOURCES = [
     "sm100/fwd_tc.cu",
     "sm100/bwd_tc.cu",
     "sm100/bwd_dq_tc.cu",
+    "sm100/bwd_wide_tc.cu",
     "sm100/decode.cu",
 ]
 

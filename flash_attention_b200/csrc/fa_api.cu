@@ -37,6 +37,8 @@ int decode_status(bool clear);
 int bwd_tc_status(bool clear);
 int bwd_dq_tc_main(const FaBwdArgs& a, cudaStream_t st);
 int bwd_dq_tc_status(bool clear);
+int bwd_wide_tc_main(const FaBwdArgs& a, cudaStream_t st);
+int bwd_wide_tc_status(bool clear);
 }  // namespace fa
 
 namespace fa_host {
@@ -98,7 +100,7 @@ extern "C" {
 const char* fa_last_error(void) { return fa_host::g_err; }
 
 const char* fa_build_info(void) {
-  return "libfa_b200 arch=sm_100a kernels=fwd_tc(tcgen05+TMA),bwd_dkdv_tc(tcgen05+TMA),bwd_dq_tc(tcgen05+TMA),decode_splitkv(TMA),"
+  return "libfa_b200 arch=sm_100a kernels=fwd_tc(tcgen05+TMA),bwd_dkdv_tc(tcgen05+TMA),bwd_dq_tc(tcgen05+TMA),bwd_wide_tc(tcgen05+TMA),decode_splitkv(TMA),"
          "fwd_generic(mma.sync),bwd_generic(mma.sync),combine,merge_partial,rotary,bwd_dot_do_o,bwd_convert_dq,kvcache_prep";
 }
 
@@ -107,7 +109,8 @@ int fa_device_status(void) {
   int d = fa::decode_status(true);
   int w = fa::bwd_tc_status(true);
   int q = fa::bwd_dq_tc_status(true);
-  return s ? s : (w ? w : (q ? q : d));
+  int x = fa::bwd_wide_tc_status(true);
+  return s ? s : (w ? w : (q ? q : (x ? x : d)));
 }
 
 int fa_abi_struct_size(int32_t which) {
@@ -213,6 +216,7 @@ int fa_bwd(const FaBwdArgs* a, fa_stream_t stream) {
   int rc = fa::bwd_pre(*a, tc ? 0 : 1, st);
   if (rc) return rc;
   if (tc) {
+    if (a->head_dim > 128) return fa::bwd_wide_tc_main(*a, st);  // one pass per output
     rc = fa::bwd_tc_main(*a, st);
     if (rc) return rc;
     return fa::bwd_dq_tc_main(*a, st);

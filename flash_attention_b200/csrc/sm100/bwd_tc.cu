@@ -559,7 +559,7 @@ int launch_bwd_tc(const FaBwdArgs& a, cudaStream_t st) {
 }  // namespace
 
 bool bwd_tc_eligible(const FaBwdArgs& a) {
-  if (a.head_dim > 128 || a.p_dropout > 0.f) return false;
+  if (a.head_dim > 256 || a.p_dropout > 0.f) return false;  // head dims 129..256 run in bwd_wide_tc.cu
   if (a.seqlen_k <= 0 || a.seqlen_q <= 0) return false;
   if (!tma_compatible(a.q) || !tma_compatible(a.k) || !tma_compatible(a.v) || !tma_compatible(a.dout)) return false;
   // the epilogues store 16 bytes at a time
