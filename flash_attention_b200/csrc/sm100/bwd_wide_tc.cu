@@ -242,6 +242,18 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_wide_tc_kernel(const __grid_c
                     (a.window_right >= 0 && r0 + kR - 1 > c0 + si.shift + a.window_right) ||
                     (a.window_left >= 0 && r0 < c0 + kN - 1 + si.shift - a.window_left);
       }
+      // ---- X2 completes first (see the MMA issuer): it is taken into registers right away so that X2(it+1) can go
+      uint32_t d[32];
+      if (PASS != PASS_DV) {
+        ok = mbar_wait(bar_x2, it & 1, W_W_X2, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        tmem_ld32(tX2, d);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_x2read);  // X2(it) is in registers: X2(it+1) may overwrite it
+      }
       // ---- P = exp2(X1 * scale - LSE), 32 streamed columns per thread, kept in registers
       ok = mbar_wait(bar_x1, it & 1, W_W_X1, abort_flag);
       if (!ok) break;
@@ -278,15 +290,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_wide_tc_kernel(const __grid_c
         for (int c = 0; c < 32; c += 2) pk[c >> 1] = Pack<T>::two(p[c], p[c + 1]);
       } else {
         // ---- dS = P o (X2 - D)
-        ok = mbar_wait(bar_x2, it & 1, W_W_X2, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        uint32_t d[32];
-        tmem_ld32(tX2, d);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_x2read);  // X2(it) is in registers: X2(it+1) may overwrite it
         if (kRowsAreQueries) {
 #pragma unroll
           for (int c = 0; c < 32; c += 2)
@@ -422,10 +425,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_wide_tc_kernel(const __grid_c
       }
     } else if (warp == kWarpMma) {
       // -------------------------------------------------------------- MMA issuer
-      // Order per block j (passes dK / dQ): X2(j+1) once the compute warps hold X2(j) in registers,
-      // X1(j+1) once they hold X1(j), then the last product of block j once W(j) is in its buffer.  X2 goes
-      // first because its tile has been resident the longest: the tile of X1(j+1) only starts loading when
-      // the last product of block j-1 completes, and X2(j+1) covers that latency.
+      // Order per block j (passes dK / dQ): X2(j+1) once the compute warps hold X2(j) in registers, the last
+      // product of block j once W(j) is in its buffer, X1(j+1) once they hold X1(j).  The tile of X1(j+2) can only
+      // start loading when the last product of block j completes (two slots); with X1 last in the order it has
+      // X1(j+1), X2(j+2) and the last product of block j+1 to arrive behind.
       if (lane == 0 && run) {
         constexpr int F = WFmt<T>::kIdesc;
         constexpr uint32_t idesc_x = make_idesc(kR, kN, F, 0, 0);    // X1, X2: K-major x K-major, N = 64 streamed rows
@@ -470,9 +473,26 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_wide_tc_kernel(const __grid_c
           if (PASS == PASS_DV) tc_commit(bar_b1_empty(0));
         }
         for (int j = 0; j < iters && ok; ++j) {
-          if (j + 1 < iters) {
-            const int n1 = (j + 1) % NS1, n2 = (j + 1) % NS2;
-            if (PASS != PASS_DV) {
+          const bool more = j + 1 < iters;
+          const int n1 = (j + 1) % NS1, n2 = (j + 1) % NS2;
+          if (PASS == PASS_DV) {
+            if (more) {
+              ok = mbar_wait(bar_x1read, j & 1, W_W_READ, abort_flag);
+              if (ok) ok = mbar_wait(bar_b1_full(n1), ((j + 1) / NS1) & 1, W_W_B_FULL, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              issue_x(C::COL_X1, oA1, oB1 + n1 * kTileB16);
+              tc_commit(bar_x1);
+              tc_commit(bar_b1_empty(n1));
+            }
+            ok = mbar_wait(bar_w, j & 1, W_W_W, abort_flag);
+            if (ok) ok = mbar_wait(bar_b2_full(j % NS2), (j / NS2) & 1, W_W_B_FULL, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_out(j, oB2 + (j % NS2) * kTileB16);
+            tc_commit(bar_b2_empty(j % NS2));
+          } else {
+            if (more) {
               ok = mbar_wait(bar_x2read, j & 1, W_W_READ, abort_flag);
               if (ok) ok = mbar_wait(bar_b2_full(n2), ((j + 1) / NS2) & 1, W_W_B_FULL, abort_flag);
               if (!ok) break;
@@ -481,24 +501,19 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_wide_tc_kernel(const __grid_c
               tc_commit(bar_x2);
               tc_commit(bar_b2_empty(n2));
             }
-            ok = mbar_wait(bar_x1read, j & 1, W_W_READ, abort_flag);
-            if (ok) ok = mbar_wait(bar_b1_full(n1), ((j + 1) / NS1) & 1, W_W_B_FULL, abort_flag);
+            ok = mbar_wait(bar_w, j & 1, W_W_W, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            issue_x(C::COL_X1, oA1, oB1 + n1 * kTileB16);
-            tc_commit(bar_x1);
-            if (PASS == PASS_DV) tc_commit(bar_b1_empty(n1));
-          }
-          ok = mbar_wait(bar_w, j & 1, W_W_W, abort_flag);
-          if (ok && PASS == PASS_DV) ok = mbar_wait(bar_b2_full(j % NS2), (j / NS2) & 1, W_W_B_FULL, abort_flag);
-          if (!ok) break;
-          tc_fence_after();
-          if (PASS == PASS_DV) {
-            issue_out(j, oB2 + (j % NS2) * kTileB16);
-            tc_commit(bar_b2_empty(j % NS2));
-          } else {
             issue_out(j, oB1 + (j % NS1) * kTileB16);
-            tc_commit(bar_b1_empty(j % NS1));
+            tc_commit(bar_b1_empty(j % NS1));  // the tile of X1(j+2) starts loading when this completes
+            if (more) {
+              ok = mbar_wait(bar_x1read, j & 1, W_W_READ, abort_flag);
+              if (ok) ok = mbar_wait(bar_b1_full(n1), ((j + 1) / NS1) & 1, W_W_B_FULL, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              issue_x(C::COL_X1, oA1, oB1 + n1 * kTileB16);
+              tc_commit(bar_x1);
+            }
           }
         }
         if (ok) tc_commit(bar_done);
