@@ -426,7 +426,11 @@ def main():
     # the backward pass dominates a step: two tensor-core kernels of similar length (dK/dV per key
     # block, dQ per query block) after one small bandwidth kernel (dot_do_o, a few percent: see
     # profiles/).  FLOPs are the algorithmic 5 GEMMs; the two kernels execute 7 (S and dP twice).
-    roofline = {"bound": "tensor", "kernel": "backward (bwd_dot_do_o + bwd_tc_kernel [dK,dV] + bwd_dq_tc_kernel [dQ])",
+    # Head dims above 128 run one kernel as three passes (dV, dK, dQ), which execute 8 GEMMs (S three times, dP twice).
+    wide = D > 128
+    bwd_kernels = ("backward (bwd_dot_do_o + bwd_wide_tc_kernel x3 [dV, dK, dQ passes])" if wide else
+                   "backward (bwd_dot_do_o + bwd_tc_kernel [dK,dV] + bwd_dq_tc_kernel [dQ])")
+    roofline = {"bound": "tensor", "kernel": bwd_kernels,
                 "achieved": tf_bwd, "peak": pk["tflops_burst"], "unit": "TFLOP/s",
                 "frac": tf_bwd / pk["tflops_burst"], "traffic": NCU_DRAM_BYTES_PER_BACKWARD.get(wl), "peak_source": pk["source"],
                 "forward": {"kernel": "fwd_tc_kernel", "achieved": tf_fwd, "frac": tf_fwd / pk["tflops_burst"],
@@ -499,7 +503,7 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOPS/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e, "pipeline": "copy of step i+1 overlaps compute of step i (2 input buffers)"},
-            "gpu_launches": args.steps * 4,
+            "gpu_launches": args.steps * (5 if wide else 4),
             "clocks": clk.summary(), "device_status": status,
         }
         print(json.dumps(line))
