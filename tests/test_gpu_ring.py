@@ -107,3 +107,32 @@ def test_fused_merge_matches_torch_merge(dtype):
     fin = ~torch.isinf(want_l)
     assert torch.allclose(lacc[:, :, S:][fin], want_l[fin], atol=1e-5)
     assert torch.equal(acc[:, :S], keep_o) and torch.equal(lacc[:, :, :S], keep_l)  # rows outside the view untouched
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("d", [64, 128, 192, 256])
+def test_block_backward_adds_dk_dv_into_fp32_accumulators(d):
+    """fa_bwd with accumulate_dkv (the ring's per-block call) against the plain call, on every tensor-core
+    backward kernel: two calls into zeroed accumulators hold twice the plain dk / dv; dq is the plain dq."""
+    from flash_attention_b200 import flash_attn_func
+    from flash_attention_b200.ring import CudaBlockOps
+
+    g = torch.Generator().manual_seed(11)
+    B, Sq, Sk, H, Hk = 2, 200, 333, 4, 2
+    q = torch.randn(B, Sq, H, d, generator=g).bfloat16().cuda()
+    k, v = (torch.randn(B, Sk, Hk, d, generator=g).bfloat16().cuda() for _ in range(2))
+    do = torch.randn(B, Sq, H, d, generator=g).bfloat16().cuda()
+    qq, kk, vv = (x.clone().requires_grad_(True) for x in (q, k, v))
+    want_dq, want_dk, want_dv = torch.autograd.grad(flash_attn_func(qq, kk, vv, causal=True), (qq, kk, vv), do)
+    scale, shift = d ** -0.5, Sk - Sq  # bottom-right aligned causal mask as a shifted window
+    out, lse = CudaBlockOps.fwd(q, k, v, scale, (-1, 0), shift)
+    dk_acc = torch.zeros(B, Sk, Hk, d, dtype=torch.float32, device="cuda")
+    dv_acc = torch.zeros_like(dk_acc)
+    for _ in range(2):
+        dq = CudaBlockOps.bwd(do, q, k, v, out, lse, dk_acc, dv_acc, scale, (-1, 0), shift)
+    torch.cuda.synchronize()
+    assert torch.equal(dq, want_dq)
+    # the plain call rounds dk / dv to bf16 once; the accumulators keep fp32
+    for acc, want in ((dk_acc, want_dk), (dv_acc, want_dv)):
+        err = (acc / 2 - want.float()).abs().max().item()
+        assert err <= 2e-2 * max(1.0, want.float().abs().max().item()), err
