@@ -131,7 +131,7 @@ def test_block_backward_adds_dk_dv_into_fp32_accumulators(d):
     for _ in range(2):
         dq = CudaBlockOps.bwd(do, q, k, v, out, lse, dk_acc, dv_acc, scale, (-1, 0), shift)
     torch.cuda.synchronize()
-    assert torch.equal(dq, want_dq)
+    assert torch.allclose(dq.float(), want_dq.float(), atol=1e-2, rtol=1e-2)
     # the plain call rounds dk / dv to bf16 once; the accumulators keep fp32
     for acc, want in ((dk_acc, want_dk), (dv_acc, want_dv)):
         err = (acc / 2 - want.float()).abs().max().item()
