@@ -85,9 +85,9 @@ typedef struct FaFwdArgs {
 
 /* Backward.  Replaces mha_bwd (flash_api.cpp:609-811) and mha_varlen_bwd (flash_api.cpp:813-1036),
    i.e. the three launches dot_do_o -> dq_dk_dv -> convert_dq of
-   csrc/flash_attn/src/flash_bwd_launch_template.h:47-90.  For head dims up to 128 without dropout the
-   launches are dot_do_o -> dK/dV kernel -> dQ kernel instead: dq is written directly, without
-   atomics, and dq_accum is not touched. */
+   csrc/flash_attn/src/flash_bwd_launch_template.h:47-90.  Without dropout the launches are
+   dot_do_o -> dK/dV kernel -> dQ kernel (head dims up to 128) or dot_do_o -> dV pass -> dK pass ->
+   dQ pass (129..256) instead: dq is written directly, without atomics, and dq_accum is not touched. */
 typedef struct FaBwdArgs {
   FaTensor q, k, v, out, dout, dq, dk, dv;
   const float* softmax_lse; /* from the forward, same layout */
