@@ -33,7 +33,8 @@ import torch  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the two tensor-core backward kernels, per launch pair, from the ncu
 # capture summarised in profiles/ (bwd_tc_kernel 781.6 MB + bwd_dq_tc_kernel 660.7 MB; algorithmic bytes: 1479 MB)
-NCU_DRAM_BYTES_PER_BACKWARD = {"train_b16_s2048_h16_d128_causal": 1.4423e9}
+# and of the three passes of the wide kernel (516.7 + 658.0 + 657.4 MB; algorithmic: 3 x 671 MB - 134 MB for the pass without V)
+NCU_DRAM_BYTES_PER_BACKWARD = {"train_b16_s2048_h16_d128_causal": 1.4423e9, "train_b16_s2048_h8_d256": 1.8321e9}
 
 WORKLOADS = {
     # name: (batch, seqlen, heads, heads_k, head_dim, causal, dtype)
