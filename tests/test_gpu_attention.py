@@ -96,7 +96,7 @@ def test_qkvpacked_and_kvpacked_match_unpacked():
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("causal,window", [(False, (-1, -1)), (True, (-1, -1)), (False, (50, 10))])
-@pytest.mark.parametrize("d,h,hk", [(128, 4, 4), (64, 6, 2), (96, 4, 1)])
+@pytest.mark.parametrize("d,h,hk", [(128, 4, 4), (64, 6, 2), (96, 4, 1), (192, 4, 2), (256, 2, 2)])
 def test_varlen(d, h, hk, causal, window, dtype):
     g = torch.Generator().manual_seed(d + h)
     lens_q = torch.randint(1, 400, (5,), generator=g).tolist()
