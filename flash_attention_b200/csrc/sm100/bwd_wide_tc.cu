@@ -15,8 +15,7 @@
 // MN-major.  No atomics: every output element is written by exactly one CTA.
 //
 // Warps: 0-7 compute (warpgroup w handles streamed columns [32w, 32w+32) of a block; in the
-// epilogue, head-dim columns [128w, 128w+128)), 8 = TMA producer, 9 = MMA issuer, 10 = TMEM owner,
-// 11 idle (setmaxnreg is a warpgroup-wide instruction).
+// epilogue, head-dim columns [128w, 128w+128)), 8 = TMA producer, 9 and 11 = MMA issuers, 10 = TMEM owner.
 #include <cstdlib>
 
 #include "../fa_common.cuh"
@@ -36,7 +35,7 @@ constexpr int kChunkA = kR * 128;        // [128 rows][64 x 16-bit]
 constexpr int kChunkB = kN * 128;        // [64 rows][64 x 16-bit]
 constexpr int kTileA = 4 * kChunkA, kTileB = 4 * kChunkB;
 constexpr int kThreads = 384;
-constexpr int kWarpProducer = 8, kWarpMma = 9, kWarpTmem = 10;
+constexpr int kWarpProducer = 8, kWarpMma = 9, kWarpTmem = 10, kWarpMmaX1 = 11;
 constexpr int kRegsCompute = 200, kRegsOther = 72;
 
 enum Pass { PASS_DV = 0, PASS_DK = 1, PASS_DQ = 2 };
@@ -423,12 +422,17 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_wide_tc_kernel(const __grid_c
           }
         }
       }
-    } else if (warp == kWarpMma) {
+    } else if (warp == kWarpMma || warp == kWarpMmaX1) {
       // -------------------------------------------------------------- MMA issuer
-      // Order per block j (passes dK / dQ): X2(j+1) once the compute warps hold X2(j) in registers, the last
-      // product of block j once W(j) is in its buffer, X1(j+1) once they hold X1(j).  The tile of X1(j+2) can only
-      // start loading when the last product of block j completes (two slots); with X1 last in the order it has
-      // X1(j+1), X2(j+2) and the last product of block j+1 to arrive behind.
+      // Two issuing threads: warp 11 issues the X1 products, warp 9 the X2 products and the last product of every
+      // block.  MMAs of different threads are not ordered among themselves, and need not be: each group waits on the
+      // barriers of what it reads and overwrites.  One thread alone is blocked while the pipe works through its
+      // MMAs (an N = 64 MMA costs it 56 cycles, two threads together 48 per MMA) and cannot look at the next
+      // group's barriers meanwhile.
+      //   X1(j+1): once the compute warps hold X1(j) in registers and the tile has landed
+      //   X2(j+1): once they hold X2(j) and its tile has landed
+      //   last product of block j: once W(j) is in its buffer; its commit releases the tile X1(j) read as well
+      //   (X1(j) is complete by then: W(j) was computed from it)
       if (lane == 0 && run) {
         constexpr int F = WFmt<T>::kIdesc;
         constexpr uint32_t idesc_x = make_idesc(kR, kN, F, 0, 0);    // X1, X2: K-major x K-major, N = 64 streamed rows
@@ -444,108 +448,66 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_wide_tc_kernel(const __grid_c
         auto koff_a = [](int kk) { return (uint32_t)(((kk >> 2) * kChunkA + (kk & 3) * 32) >> 4); };
         auto koff_b = [](int kk) { return (uint32_t)(((kk >> 2) * kChunkB + (kk & 3) * 32) >> 4); };
         auto moff = [](int kk) { return (uint32_t)((kk * 2048) >> 4) + kMn; };  // MN-major k-step: 16 rows of 128 bytes
-        // Every barrier is tested while the MMAs of the group before its use are being issued (the issue of a
-        // group takes about as long as its execution, the tensor pipe's queue is short), and the answer is
-        // consumed afterwards (mbar_test / mbar_wait_probed): a lone thread's round trip to a barrier costs
-        // ~130 cycles, which would otherwise be paid with an empty pipe.  bar == 0: nothing to test.
-        struct Probe {
-          uint32_t bar0, par0, bar1, par1;
-        };
-        uint32_t hit0 = 0, hit1 = 0;
-        auto probe = [&](const Probe& pr) {
-          hit0 = pr.bar0 ? mbar_test(pr.bar0, pr.par0) : 0u;
-          hit1 = pr.bar1 ? mbar_test(pr.bar1, pr.par1) : 0u;
-        };
-        auto issue_x = [&](uint32_t d_col, uint32_t a_lo, uint32_t b_lo, const Probe& pr) {
+        auto issue_x = [&](uint32_t d_col, uint32_t a_lo, uint32_t b_lo) {
 #pragma unroll
-          for (int kk = 0; kk < kDH / 16; ++kk) {
-            if (kk == kDH / 16 - 4) probe(pr);
+          for (int kk = 0; kk < kDH / 16; ++kk)
             mma_ss(tmem + d_col, dsc(a_lo + koff_a(kk)), dsc(b_lo + koff_b(kk)), idesc_x, kk > 0);
-          }
         };
-        auto issue_out = [&](int j, uint32_t b_lo, const Probe& pr) {
+        auto issue_out = [&](int j, uint32_t b_lo) {
           // the two warpgroups' halves of W are the two 16-column halves of this block's buffer
 #pragma unroll
-          for (int kk = 0; kk < kN / 16; ++kk) {
-            if (kk == 2) probe(pr);
+          for (int kk = 0; kk < kN / 16; ++kk)
             mma_ts(tmem + C::COL_OUT, tmem + C::COL_W + (j & 1) * 32 + kk * 8, dsc(b_lo + moff(kk)), idesc_o, (j > 0) || kk > 0);
-          }
         };
-        const Probe no_probe{0u, 0u, 0u, 0u};
         bool ok = mbar_wait(bar_a, 0, W_W_A, abort_flag);
-        if (PASS != PASS_DV) {
-          if (ok) ok = mbar_wait(bar_b2_full(0), 0, W_W_B_FULL, abort_flag);
-          if (ok) {
-            tc_fence_after();
-            issue_x(C::COL_X2, oA2, oB2, no_probe);
-            tc_commit(bar_x2);
-            tc_commit(bar_b2_empty(0));
-          }
-        }
-        if (ok) ok = mbar_wait(bar_b1_full(0), 0, W_W_B_FULL, abort_flag);
-        if (ok) {
-          tc_fence_after();
-          issue_x(C::COL_X1, oA1, oB1, no_probe);
-          tc_commit(bar_x1);
-          if (PASS == PASS_DV) tc_commit(bar_b1_empty(0));
-        }
-        hit0 = hit1 = 0;
-        for (int j = 0; j < iters && ok; ++j) {
-          const bool more = j + 1 < iters, more2 = j + 2 < iters;
-          const int n1 = (j + 1) % NS1, n2 = (j + 1) % NS2;
-          const uint32_t p1 = ((j + 1) / NS1) & 1, p2 = ((j + 1) / NS2) & 1;
-          if (PASS == PASS_DV) {
-            // hits on entry: x1read(j), b1_full(j+1)   (tested while the last product of block j-1 was issued)
-            if (more) {
-              ok = mbar_wait_probed(hit0, bar_x1read, j & 1, W_W_READ, abort_flag);
-              if (ok) ok = mbar_wait_probed(hit1, bar_b1_full(n1), p1, W_W_B_FULL, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-              issue_x(C::COL_X1, oA1, oB1 + n1 * kTileB16, Probe{bar_w, (uint32_t)(j & 1), bar_b2_full(j % NS2), (uint32_t)((j / NS2) & 1)});
-              tc_commit(bar_x1);
-              tc_commit(bar_b1_empty(n1));
-            } else {
-              hit0 = hit1 = 0;
-            }
-            ok = mbar_wait_probed(hit0, bar_w, j & 1, W_W_W, abort_flag);
-            if (ok) ok = mbar_wait_probed(hit1, bar_b2_full(j % NS2), (j / NS2) & 1, W_W_B_FULL, abort_flag);
+        if (warp == kWarpMmaX1) {
+          // ---- X1 products
+          for (int j = 0; j < iters && ok; ++j) {
+            const int s1 = j % NS1;
+            if (j > 0) ok = mbar_wait(bar_x1read, (j - 1) & 1, W_W_READ, abort_flag);
+            if (ok) ok = mbar_wait(bar_b1_full(s1), (j / NS1) & 1, W_W_B_FULL, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            issue_out(j, oB2 + (j % NS2) * kTileB16,
-                      more2 ? Probe{bar_x1read, (uint32_t)((j + 1) & 1), bar_b1_full((j + 2) % NS1), (uint32_t)(((j + 2) / NS1) & 1)}
-                            : (more ? Probe{bar_x1read, (uint32_t)((j + 1) & 1), 0u, 0u} : no_probe));
-            if (!more2) hit1 = 0;
-            tc_commit(bar_b2_empty(j % NS2));
-          } else {
-            // hits on entry: x2read(j), b2_full(j+1)   (tested while X1(j) was issued)
-            if (more) {
-              ok = mbar_wait_probed(hit0, bar_x2read, j & 1, W_W_READ, abort_flag);
-              if (ok) ok = mbar_wait_probed(hit1, bar_b2_full(n2), p2, W_W_B_FULL, abort_flag);
+            issue_x(C::COL_X1, oA1, oB1 + s1 * kTileB16);
+            tc_commit(bar_x1);
+            if (PASS == PASS_DV) tc_commit(bar_b1_empty(s1));
+          }
+        } else {
+          // ---- X2 products and the last product of every block
+          if (PASS != PASS_DV) {
+            if (ok) ok = mbar_wait(bar_b2_full(0), 0, W_W_B_FULL, abort_flag);
+            if (ok) {
+              tc_fence_after();
+              issue_x(C::COL_X2, oA2, oB2);
+              tc_commit(bar_x2);
+              tc_commit(bar_b2_empty(0));
+            }
+          }
+          for (int j = 0; j < iters && ok; ++j) {
+            if (PASS != PASS_DV && j + 1 < iters) {
+              const int n2 = (j + 1) % NS2;
+              ok = mbar_wait(bar_x2read, j & 1, W_W_READ, abort_flag);
+              if (ok) ok = mbar_wait(bar_b2_full(n2), ((j + 1) / NS2) & 1, W_W_B_FULL, abort_flag);
               if (!ok) break;
               tc_fence_after();
-              issue_x(C::COL_X2, oA2, oB2 + n2 * kTileB16, Probe{bar_w, (uint32_t)(j & 1), 0u, 0u});
+              issue_x(C::COL_X2, oA2, oB2 + n2 * kTileB16);
               tc_commit(bar_x2);
               tc_commit(bar_b2_empty(n2));
-            } else {
-              hit0 = 0;
             }
-            ok = mbar_wait_probed(hit0, bar_w, j & 1, W_W_W, abort_flag);
+            ok = mbar_wait(bar_w, j & 1, W_W_W, abort_flag);
+            if (ok && PASS == PASS_DV) ok = mbar_wait(bar_b2_full(j % NS2), (j / NS2) & 1, W_W_B_FULL, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            issue_out(j, oB1 + (j % NS1) * kTileB16, more ? Probe{bar_x1read, (uint32_t)(j & 1), bar_b1_full(n1), p1} : no_probe);
-            tc_commit(bar_b1_empty(j % NS1));  // the tile of X1(j+2) starts loading when this completes
-            if (more) {
-              ok = mbar_wait_probed(hit0, bar_x1read, j & 1, W_W_READ, abort_flag);
-              if (ok) ok = mbar_wait_probed(hit1, bar_b1_full(n1), p1, W_W_B_FULL, abort_flag);
-              if (!ok) break;
-              tc_fence_after();
-              issue_x(C::COL_X1, oA1, oB1 + n1 * kTileB16,
-                      more2 ? Probe{bar_x2read, (uint32_t)((j + 1) & 1), bar_b2_full((j + 2) % NS2), (uint32_t)(((j + 2) / NS2) & 1)} : no_probe);
-              tc_commit(bar_x1);
+            if (PASS == PASS_DV) {
+              issue_out(j, oB2 + (j % NS2) * kTileB16);
+              tc_commit(bar_b2_empty(j % NS2));
+            } else {
+              issue_out(j, oB1 + (j % NS1) * kTileB16);
+              tc_commit(bar_b1_empty(j % NS1));
             }
           }
+          if (ok) tc_commit(bar_done);
         }
-        if (ok) tc_commit(bar_done);
       }
     }
   }
