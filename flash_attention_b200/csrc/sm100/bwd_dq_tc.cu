@@ -32,7 +32,7 @@ namespace {
 constexpr int kB = 128;                 // query rows per CTA == keys per block
 constexpr int kChunkBytes = 128 * 128;  // [128 rows][64 x 16-bit]
 constexpr int kThreads = 384;
-constexpr int kWarpProducer = 8, kWarpMma = 9, kWarpTmem = 10;
+constexpr int kWarpProducer = 8, kWarpMma = 9, kWarpTmem = 10, kWarpMmaDq = 11;
 constexpr int kRegsCompute = 200, kRegsOther = 72;
 
 enum DqWait { W_Q_ALIGN = 40, W_Q_QDO = 41, W_Q_KV_FULL = 42, W_Q_KV_EMPTY = 43, W_Q_S = 44, W_Q_DP = 45, W_Q_DS = 46,
@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
         for (int i = 0; i < 6; ++i) atomicAdd(&g_dq_t[16 + i], (unsigned long long)tm[i]);
 #endif
       }
-    } else if (warp == kWarpMma) {
+    } else if (warp == kWarpMma || warp == kWarpMmaDq) {
       // -------------------------------------------------------------- MMA issuer
       // Each MMA group is issued as soon as its inputs exist and its output columns are free:
       //   S(j+1) once the compute warps hold S(j) in registers, dP(j+1) once they hold dP(j),
@@ -367,94 +367,38 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
           tc_commit(bar);
         };
         bool ok = mbar_wait(bar_qdo, 0, W_Q_QDO, abort_flag);
-        if (ok) ok = mbar_wait(bar_k_full(0), 0, W_Q_KV_FULL, abort_flag);
-        if (ok) {
-          tc_fence_after();
-          issue_s(C::COL_S, oQ, oK, bar_s);
-        }
-        if (ok) ok = mbar_wait(bar_v_full(0), 0, W_Q_KV_FULL, abort_flag);
-        if (ok) {
-          tc_fence_after();
-          issue_s(C::COL_DP, oDO, oV, bar_dp);
-          tc_commit(bar_v_empty(0));
-        }
-#ifdef FA_BWD_TIMERS
-        long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
-        const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-#endif
-        int ks = 0, nks = 1 % NSK, nvs = 1 % NSV;  // ring positions of K(j), K(j+1), V(j+1)
-        uint32_t kph = 0, vph = (1 / NSV) & 1;      // phase of K(j+1)'s / V(j+1)'s full barrier
-        if (nks == 0) kph ^= 1;
-        // every barrier is tested one MMA group ahead of its use (see mbar_test)
-        uint32_t h_sread = mbar_test(bar_sread, 0), h_k = mbar_test(bar_k_full(nks), kph), h_dpread = 0, h_v = 0, h_ds = 0;
-        for (int j = 0; j < iters && ok; ++j) {
-          const bool more = j + 1 < iters;
-          TRC(15);
-          if (more) {
-            ok = mbar_wait_probed(h_sread, bar_sread, j & 1, W_Q_S, abort_flag);
-            TMR(6);
-            TRC(8);
-            if (ok) ok = mbar_wait_probed(h_k, bar_k_full(nks), kph, W_Q_KV_FULL, abort_flag);
+        if (warp == kWarpMma) {
+          // ---- S and dP: block j+1 as soon as the compute warps hold block j's in registers
+          for (int j = 0; j < iters && ok; ++j) {
+            const int ks = j % NSK, vs = j % NSV;
+            if (j > 0) ok = mbar_wait(bar_sread, (j - 1) & 1, W_Q_S, abort_flag);
+            if (ok) ok = mbar_wait(bar_k_full(ks), (j / NSK) & 1, W_Q_KV_FULL, abort_flag);
             if (!ok) break;
-            TMR(0);
-            TRC(9);
             tc_fence_after();
-            h_dpread = mbar_test(bar_dpread, j & 1);
-            h_v = mbar_test(bar_v_full(nvs), vph);
-            issue_s(C::COL_S, oQ, oK + nks * kTile16, bar_s);
-            TMR(1);
-            TRC(10);
-#ifdef FA_BWD_TIMERS
-            *t_mark = clock64();
-#endif
-            ok = mbar_wait_probed(h_dpread, bar_dpread, j & 1, W_Q_DP, abort_flag);
-            if (ok) ok = mbar_wait_probed(h_v, bar_v_full(nvs), vph, W_Q_KV_FULL, abort_flag);
+            issue_s(C::COL_S, oQ, oK + ks * kTile16, bar_s);
+            if (j > 0) ok = mbar_wait(bar_dpread, (j - 1) & 1, W_Q_DP, abort_flag);
+            if (ok) ok = mbar_wait(bar_v_full(vs), (j / NSV) & 1, W_Q_KV_FULL, abort_flag);
             if (!ok) break;
-            TMR(2);
-            TRC(11);
             tc_fence_after();
-            h_ds = mbar_test(bar_ds, j & 1);
-            issue_s(C::COL_DP, oDO, oV + nvs * kTile16, bar_dp);
-            tc_commit(bar_v_empty(nvs));
-            TMR(3);
-            TRC(12);
-          } else {
-            h_ds = mbar_test(bar_ds, j & 1);
+            issue_s(C::COL_DP, oDO, oV + vs * kTile16, bar_dp);
+            tc_commit(bar_v_empty(vs));
           }
-          ok = mbar_wait_probed(h_ds, bar_ds, j & 1, W_Q_DS, abort_flag);
-          if (!ok) break;
-          TMR(4);
-          TRC(13);
-          tc_fence_after();
-          const int ks_now = ks;
-          ks = nks;
-          if (++nks == NSK) {
-            nks = 0;
-            kph ^= 1;
-          }
-          if (++nvs == NSV) {
-            nvs = 0;
-            vph ^= 1;
-          }
-          if (j + 2 < iters) {
-            h_sread = mbar_test(bar_sread, (j + 1) & 1);
-            h_k = mbar_test(bar_k_full(nks), kph);
-          }
-          // dQ += dS K: the two warpgroups' halves of dS are the two 32-column halves of this block's buffer
+        } else {
+          // ---- dQ += dS K: the two warpgroups' halves of dS are the two 32-column halves of the block's buffer.
+          // Its commit releases the K tile, which S(j) of the other issuer read as well: dS(j) was computed from S(j).
+          for (int j = 0; j < iters && ok; ++j) {
+            const int ks = j % NSK;
+            ok = mbar_wait(bar_ds, j & 1, W_Q_DS, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
-          for (int kk = 0; kk < kB / 16; ++kk)
-            mma_ts(tmem + C::COL_DQ, tmem + C::COL_DS + (j & 1) * 64 + kk * 8, dsc(oK + ks_now * kTile16 + moff(kk)), idesc_dq,
-                   (j > 0) || kk > 0);
-          tc_commit(bar_k_empty(ks_now));
-          TMR(5);
-          TRC(14);
+            for (int kk = 0; kk < kB / 16; ++kk)
+              mma_ts(tmem + C::COL_DQ, tmem + C::COL_DS + (j & 1) * 64 + kk * 8, dsc(oK + ks * kTile16 + moff(kk)), idesc_dq,
+                     (j > 0) || kk > 0);
+            tc_commit(bar_k_empty(ks));
+          }
+          if (ok) tc_commit(bar_done);
         }
-#ifdef FA_BWD_TIMERS
-        for (int i = 0; i < 6; ++i) atomicAdd(&g_dq_t[8 + i], (unsigned long long)tm[i]);
-        atomicAdd(&g_dq_t[14], (unsigned long long)tm[6]);
-        atomicAdd(&g_dq_t[15], (unsigned long long)iters);
-#endif
-        if (ok) tc_commit(bar_done);
       }
     }
   }
