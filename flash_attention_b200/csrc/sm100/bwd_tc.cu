@@ -40,7 +40,7 @@ constexpr int kB = 128;                 // query rows per block == keys per CTA
 constexpr int kChunkBytes = 128 * 128;  // [128 rows][64 x 16-bit]
 
 constexpr int kThreads = 384;
-constexpr int kWarpProducer = 8, kWarpMma = 9, kWarpStats = 10;
+constexpr int kWarpProducer = 8, kWarpMma = 9, kWarpStats = 10, kWarpMmaS = 11;
 constexpr int kRegsCompute = 200, kRegsOther = 72;
 
 enum BwdWait { W_B_KV = 21, W_B_QDO_FULL = 22, W_B_QDO_EMPTY = 23, W_B_STATS_FULL = 24, W_B_STATS_EMPTY = 25,
@@ -409,11 +409,12 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
           fetch();
         }
       }
-    } else if (warp == kWarpMma) {
+    } else if (warp == kWarpMma || warp == kWarpMmaS) {
       // -------------------------------------------------------------- MMA issuer
-      // Order on the tensor pipe, block i:  S^T(i+1) | dV(i) | dK(i) dP^T(i+1)
-      //   S^T(i+1) is issued as soon as the compute warps hold S^T(i) in registers;
-      //   dV(i) waits for P^T(i), dK(i) for dS^T(i); both sit over dP^T(i), so dP^T(i+1) follows dK(i).
+      // Two issuing threads.  Warp 11 issues S^T(i+1) as soon as the compute warps hold S^T(i) in registers.  Warp 9
+      // issues the chain dV(i) | dK(i) | dP^T(i+1): dV(i) waits for P^T(i), dK(i) for dS^T(i); both sit over dP^T(i),
+      // and the MMAs of one thread execute in order, so dP^T(i+1) overwrites them only after they were read.
+      // MMAs of the two threads are not ordered among themselves and need not be.
       if (lane == 0 && run) {
         constexpr int F = BFmt<T>::kIdesc;
         constexpr uint32_t idesc_st = make_idesc(kB, kB, F, 0, 0);   // S^T, dP^T: K-major x K-major, N = 128 queries
@@ -434,65 +435,51 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
           tc_commit(bar);
         };
         bool ok = mbar_wait(bar_kv, 0, W_B_KV, abort_flag);
-        if (ok) ok = mbar_wait(bar_q_full(0), 0, W_B_QDO_FULL, abort_flag);
-        if (ok) {
-          tc_fence_after();
-          issue_st(C::COL_S, oK, oQ, bar_s);
-        }
-        if (ok) ok = mbar_wait(bar_do_full(0), 0, W_B_QDO_FULL, abort_flag);
-        if (ok) {
-          tc_fence_after();
-          issue_st(C::COL_DP, oV, oDO, bar_dp);
-        }
-#ifdef FA_BWD_TIMERS
-        long long tm[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
-#endif
-        for (int it = 0; it < iters && ok; ++it) {
-          const bool more = it + 1 < iters;
-          const int qs = it % NSQ, os = it % NSO, nqs = (it + 1) % NSQ, nos = (it + 1) % NSO;
-          if (more) {
-            // S^T(it) has been read into registers: S^T(it+1) runs while P^T(it) is being computed
-            ok = mbar_wait(bar_sread, it & 1, W_B_S, abort_flag);
-            if (!ok) break;
-            TMR(0);
-            ok = mbar_wait(bar_q_full(nqs), ((it + 1) / NSQ) & 1, W_B_QDO_FULL, abort_flag);
-            if (!ok) break;
-            TMR(1);
-            tc_fence_after();
-            issue_st(C::COL_S, oK, oQ + nqs * kTile16, bar_s);
-            TMR(2);
-          }
-          // P^T(it) is in TMEM over dP^T(it): dV += P^T dO (the warpgroups' halves sit at columns 0 and 64 of
-          // the dP^T range); that was the last use of this dO tile
-          ok = mbar_wait(bar_p, it & 1, W_B_PDS, abort_flag);
-          if (!ok) break;
-          TMR(3);
-          tc_fence_after();
-#pragma unroll
-          for (int kk = 0; kk < kB / 16; ++kk)
-            mma_ts(tmem + C::COL_DV, tmem + C::COL_DP + (kk >> 2) * 64 + (kk & 3) * 8, dsc(oDO + os * kTile16 + moff(kk)),
-                   idesc_dv, (it > 0) || kk > 0);
-          tc_commit(bar_do_empty(os));
-          TMR(4);
-          // dS^T(it) is in TMEM next to P^T(it) (columns 32 and 96 of the dP^T range): dK += dS^T Q, the last
-          // use of this Q tile; after it the next dP^T may overwrite the range
-          ok = mbar_wait(bar_ds, it & 1, W_B_PDS, abort_flag);
-          if (!ok) break;
-          TMR(5);
-          tc_fence_after();
-#pragma unroll
-          for (int kk = 0; kk < kB / 16; ++kk)
-            mma_ts(tmem + C::COL_DK, tmem + C::COL_DP + 32 + (kk >> 2) * 64 + (kk & 3) * 8, dsc(oQ + qs * kTile16 + moff(kk)),
-                   idesc_dv, (it > 0) || kk > 0);
-          tc_commit(bar_q_empty(qs));
-          TMR(6);
-          if (more) {
-            ok = mbar_wait(bar_do_full(nos), ((it + 1) / NSO) & 1, W_B_QDO_FULL, abort_flag);
+        if (warp == kWarpMmaS) {
+          for (int it = 0; it < iters && ok; ++it) {
+            const int qs = it % NSQ;
+            if (it > 0) ok = mbar_wait(bar_sread, (it - 1) & 1, W_B_S, abort_flag);
+            if (ok) ok = mbar_wait(bar_q_full(qs), (it / NSQ) & 1, W_B_QDO_FULL, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            issue_st(C::COL_DP, oV, oDO + nos * kTile16, bar_dp);
+            issue_st(C::COL_S, oK, oQ + qs * kTile16, bar_s);
           }
-          TMR(7);
+        } else {
+          if (ok) ok = mbar_wait(bar_do_full(0), 0, W_B_QDO_FULL, abort_flag);
+          if (ok) {
+            tc_fence_after();
+            issue_st(C::COL_DP, oV, oDO, bar_dp);
+          }
+          for (int it = 0; it < iters && ok; ++it) {
+            const bool more = it + 1 < iters;
+            const int qs = it % NSQ, os = it % NSO, nos = (it + 1) % NSO;
+            // P^T(it) is in TMEM over dP^T(it): dV += P^T dO (the warpgroups' halves sit at columns 0 and 64 of
+            // the dP^T range); that was the last use of this dO tile
+            ok = mbar_wait(bar_p, it & 1, W_B_PDS, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < kB / 16; ++kk)
+              mma_ts(tmem + C::COL_DV, tmem + C::COL_DP + (kk >> 2) * 64 + (kk & 3) * 8, dsc(oDO + os * kTile16 + moff(kk)),
+                     idesc_dv, (it > 0) || kk > 0);
+            tc_commit(bar_do_empty(os));
+            // dS^T(it) is in TMEM next to P^T(it) (columns 32 and 96 of the dP^T range): dK += dS^T Q, the last
+            // use of this Q tile (S^T(it) of the other issuer read it too: P^T(it) was computed from it)
+            ok = mbar_wait(bar_ds, it & 1, W_B_PDS, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < kB / 16; ++kk)
+              mma_ts(tmem + C::COL_DK, tmem + C::COL_DP + 32 + (kk >> 2) * 64 + (kk & 3) * 8, dsc(oQ + qs * kTile16 + moff(kk)),
+                     idesc_dv, (it > 0) || kk > 0);
+            tc_commit(bar_q_empty(qs));
+            if (more) {
+              ok = mbar_wait(bar_do_full(nos), ((it + 1) / NSO) & 1, W_B_QDO_FULL, abort_flag);
+              if (!ok) break;
+              tc_fence_after();
+              issue_st(C::COL_DP, oV, oDO + nos * kTile16, bar_dp);
+            }
+          }
         }
 #ifdef FA_BWD_TIMERS
         for (int i = 0; i < 8; ++i) atomicAdd(&g_bwd_t[8 + i], (unsigned long long)tm[i]);
