@@ -359,7 +359,35 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
         auto in_range = [&](int t, int j) { return j >= lo[t] && j < hi[t]; };
         auto slot_of = [&](int idx) { return idx % C::STAGES; };
         auto par_of = [&](int idx) { return (uint32_t)((idx / C::STAGES) & 1); };
-        if (nblk > 0) {
+        if (C::NT == 1) {
+          // one tile per CTA: PV(j) | S(j+1) with plain waits (the tests ahead of use of the two-tile order below
+          // cost time here: there is no other tile's group to issue meanwhile)
+          if (nblk > 0) {
+            ok = mbar_wait(bar_qfull(0), 0, W_QFULL, abort_flag);
+            if (ok) ok = mbar_wait(bar_full(slot_of(0)), par_of(0), W_KVFULL, abort_flag);
+            if (ok) {
+              tc_fence_after();
+              issue_s(0, slot_of(0));
+              tc_commit(bar_empty(slot_of(0)));
+            }
+            for (int j = J_lo; j < J_hi && ok; ++j) {
+              const int iv = 2 * (j - J_lo) + 1, ik = iv + 1;  // ring indices of V(j) and K(j+1)
+              const bool more = j + 1 < J_hi;
+              ok = mbar_wait(bar_full(slot_of(iv)), par_of(iv), W_KVFULL, abort_flag);
+              if (ok && more) ok = mbar_wait(bar_full(slot_of(ik)), par_of(ik), W_KVFULL, abort_flag);
+              if (ok) ok = mbar_wait(bar_pfull(0), p_iter[0] & 1, W_PFULL, abort_flag);
+              if (!ok) break;
+              ++p_iter[0];
+              tc_fence_after();
+              issue_pv(0, slot_of(iv), j == J_lo);
+              tc_commit(bar_empty(slot_of(iv)));
+              if (more) {
+                issue_s(0, slot_of(ik));
+                tc_commit(bar_empty(slot_of(ik)));
+              }
+            }
+          }
+        } else if (nblk > 0) {
           for (int t = 0; t < 2 && ok; ++t)
             if (hi[t] > lo[t]) ok = mbar_wait(bar_qfull(t), 0, W_QFULL, abort_flag);
           // prologue: S_t(J_lo)
