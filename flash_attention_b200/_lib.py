@@ -107,6 +107,7 @@ EXPORTS = (
     "fa_fwd", "fa_bwd", "fa_fwd_kvcache", "fa_fwd_num_splits", "fa_kvcache_plan", "fa_bwd_workspace_bytes",
     "fa_combine", "fa_last_error", "fa_build_info", "fa_device_status", "fa_abi_struct_size",
     "fa_fwd_kvcache_noalloc", "fa_noalloc_scratch_bytes", "fa_merge_partial", "fa_rotary",
+    "fa_selftest_wait_timeout", "fa_selftest_device_once",
 )
 
 _lib = None
@@ -147,6 +148,10 @@ def lib():
         L.fa_last_error.restype = C.c_char_p
         L.fa_build_info.restype = C.c_char_p
         L.fa_device_status.restype = C.c_int
+        L.fa_selftest_wait_timeout.argtypes = [c_i64, c_vp]
+        L.fa_selftest_wait_timeout.restype = C.c_int
+        L.fa_selftest_device_once.argtypes = [C.POINTER(c_i32), c_i32, C.POINTER(c_i32)]
+        L.fa_selftest_device_once.restype = C.c_int
         L.fa_abi_struct_size.argtypes = [c_i32]
         L.fa_abi_struct_size.restype = C.c_int
         for which, st in enumerate((FaTensor, FaFwdArgs, FaBwdArgs, FaKvcacheArgs, FaRotaryArgs)):

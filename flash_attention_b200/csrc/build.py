@@ -26,6 +26,7 @@ SOURCES = [
     "sm100/bwd_dq_tc.cu",
     "sm100/bwd_wide_tc.cu",
     "sm100/decode.cu",
+    "sm100/status.cu",
 ]
 
 NVCC_FLAGS = [

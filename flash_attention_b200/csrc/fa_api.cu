@@ -29,16 +29,16 @@ int bwd_tc_main(const FaBwdArgs& a, cudaStream_t st);
 // fused single-token decode
 bool decode_eligible(const FaKvcacheArgs& a);
 int decode_plan(const FaKvcacheArgs& a, int num_sms);
-int decode_run(const FaKvcacheArgs& a, int num_splits, cudaStream_t st);
+int decode_run(const FaKvcacheArgs& a, int num_splits, cudaStream_t st, bool may_allocate = true);
+int decode_noalloc_fit(const FaKvcacheArgs& a, int num_splits);
 int decode_run_noalloc(const FaKvcacheArgs& a, int num_splits, cudaStream_t st);
 size_t decode_noalloc_capacity();
-int fwd_tc_status(bool clear);
-int decode_status(bool clear);
-int bwd_tc_status(bool clear);
 int bwd_dq_tc_main(const FaBwdArgs& a, cudaStream_t st);
-int bwd_dq_tc_status(bool clear);
 int bwd_wide_tc_main(const FaBwdArgs& a, cudaStream_t st);
-int bwd_wide_tc_status(bool clear);
+// device status word (sm100/status.cu)
+int status_peek();
+int status_read(bool clear);
+int selftest_wait_timeout(long long limit_cycles, int code, cudaStream_t st);
 }  // namespace fa
 
 namespace fa_host {
@@ -68,6 +68,21 @@ int sm_count() {
   }
   return cached[dev];
 }
+int raise_smem_limit(DeviceOnce& once, const void* kernel, int bytes, const char* name) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    dev = -1;
+  }
+  DeviceOnce probe = once;
+  if (!device_once_needed(probe, dev)) return 0;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    set_error("%s: cannot reserve %d bytes of shared memory: %s", name, bytes, cudaGetErrorString(cudaGetLastError()));
+    return 2;
+  }
+  device_once_needed(once, dev);
+  return 0;
+}
 static int env_flag(const char* name) {
   const char* v = getenv(name);
   return v && v[0] && v[0] != '0';
@@ -95,6 +110,18 @@ static int check_common(int batch, int sq, int sk, int heads, int heads_k, int d
   return 0;
 }
 
+// A kernel of an earlier call gave up on a bounded wait: refuse to launch until the caller has read
+// (and thereby cleared) the status, instead of returning tensors that no kernel wrote.
+static int refuse_if_device_failed() {
+  const int code = fa::status_peek();
+  if (code) {
+    set_error("an earlier kernel on this device gave up on a bounded wait (code %d) and its outputs are incomplete; "
+              "call fa_device_status() to read and clear the status before launching again", code);
+    return 3;
+  }
+  return 0;
+}
+
 extern "C" {
 
 const char* fa_last_error(void) { return fa_host::g_err; }
@@ -104,13 +131,18 @@ const char* fa_build_info(void) {
          "fwd_generic(mma.sync),bwd_generic(mma.sync),combine,merge_partial,rotary,bwd_dot_do_o,bwd_convert_dq,kvcache_prep";
 }
 
-int fa_device_status(void) {
-  int s = fa::fwd_tc_status(true);
-  int d = fa::decode_status(true);
-  int w = fa::bwd_tc_status(true);
-  int q = fa::bwd_dq_tc_status(true);
-  int x = fa::bwd_wide_tc_status(true);
-  return s ? s : (w ? w : (q ? q : (x ? x : d)));
+int fa_device_status(void) { return fa::status_read(true); }
+
+int fa_selftest_wait_timeout(int64_t limit_cycles, fa_stream_t stream) {
+  FA_REQUIRE(limit_cycles > 0 && limit_cycles <= 100000000ll, "limit_cycles must be in (0, 1e8]");
+  return fa::selftest_wait_timeout(limit_cycles, /*code=*/99, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int fa_selftest_device_once(const int32_t* devices, int32_t n, int32_t* needed) {
+  FA_REQUIRE(devices && needed && n >= 0, "null pointer");
+  fa_host::DeviceOnce once = {};
+  for (int i = 0; i < n; ++i) needed[i] = fa_host::device_once_needed(once, devices[i]) ? 1 : 0;
+  return 0;
 }
 
 int fa_abi_struct_size(int32_t which) {
@@ -183,6 +215,7 @@ int fa_fwd(const FaFwdArgs* a, fa_stream_t stream) {
     FA_REQUIRE(a->p_dropout == 0.f, "split-KV does not support dropout");
   }
   if (a->seqlen_q == 0 || a->batch == 0) return 0;
+  if (refuse_if_device_failed()) return 3;
   if (a->num_splits <= 1 && !fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::fwd_tc_eligible(*a))
     return fa::fwd_tc(*a, st);
   int rc = fa::fwd_generic(*a, st);
@@ -211,6 +244,7 @@ int fa_bwd(const FaBwdArgs* a, fa_stream_t stream) {
   FA_REQUIRE(a->p_dropout >= 0.f && a->p_dropout < 1.f, "p_dropout must be in [0, 1)");
   FA_REQUIRE(a->d_seqlen >= a->seqlen_q, "softmax_d row pitch is smaller than seqlen_q");
   if (a->seqlen_q == 0 || a->batch == 0) return 0;
+  if (refuse_if_device_failed()) return 3;
   const bool tc = a->seqlen_k > 0 && !fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::bwd_tc_eligible(*a);
   // the tensor-core path writes dq directly (two kernels: dK / dV per key block, dQ per query block)
   int rc = fa::bwd_pre(*a, tc ? 0 : 1, st);
@@ -277,6 +311,7 @@ int fa_fwd_kvcache(const FaKvcacheArgs* a, fa_stream_t stream) {
   if (splits < 0) return 1;
   if (splits > 1) FA_REQUIRE(a->lse_accum && a->out_accum, "split-KV needs lse_accum and out_accum");
   if (a->seqlen_q == 0) return 0;
+  if (refuse_if_device_failed()) return 3;
   if (!fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::decode_eligible(*a)) return fa::decode_run(*a, splits, st);
 
   // General path: append/rotate in a first launch, then the any-shape forward on the cache.
@@ -335,7 +370,10 @@ int fa_fwd_kvcache_noalloc(const FaKvcacheArgs* a, fa_stream_t stream) {
   FA_REQUIRE(a->softmax_lse != nullptr, "softmax_lse: null pointer");
   int splits = fa::decode_plan(*a, fa_host::sm_count());
   if (splits < 1) splits = 1;
+  // asked to choose: choose among the split counts whose partials fit the built-in buffer
+  if (a->num_splits == 0) splits = fa::decode_noalloc_fit(*a, splits);
   if (a->seqlen_q == 0) return 0;
+  if (refuse_if_device_failed()) return 3;
   return fa::decode_run_noalloc(*a, splits, st);
 }
 

@@ -208,6 +208,21 @@ namespace fa_host {
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);
 int sm_count();
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to one device: a kernel's launcher keeps
+// one of these (a static, zero-initialised) and raises the limit once per device, not once per process.
+struct DeviceOnce {
+  bool done[64];
+};
+// true when the caller still has to do its per-device set-up for `dev` (and marks it done); devices
+// outside the table are never marked, so their set-up simply runs on every call.
+inline bool device_once_needed(DeviceOnce& once, int dev) {
+  if (dev < 0 || dev >= 64) return true;
+  if (once.done[dev]) return false;
+  once.done[dev] = true;
+  return true;
+}
+int raise_smem_limit(DeviceOnce& once, const void* kernel, int bytes, const char* name);
 }  // namespace fa_host
 
 #define FA_REQUIRE(cond, ...)            \

@@ -16,7 +16,6 @@
 // Warps: 0-7 compute (warpgroup w handles key columns [64w, 64w+64) of the block; in the epilogue,
 // head-dim columns [D/2*w, ...)), 8 = TMA producer, 9 = MMA issuer, 10 = TMEM owner, 11 idle
 // (setmaxnreg is a warpgroup-wide instruction).
-// #define FA_BWD_TIMERS 1  // per-phase cycle counters, read through fa_bwd_timers / fa_bwd_dq_timers
 #include <cstdlib>
 
 #include "../fa_common.cuh"
@@ -26,6 +25,8 @@
 namespace fa {
 
 using namespace ptx;
+
+StatusRef status_ref(bool may_allocate);
 
 namespace {
 
@@ -51,7 +52,7 @@ struct QCfg {
   static constexpr int OFF_V = OFF_K + NSK * TILE_BYTES;
   static constexpr int OFF_BAR = OFF_V + NSV * TILE_BYTES;
   static constexpr int NBAR = 2 * NSK + 2 * NSV + 8;
-  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16;
+  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 32;
   static constexpr int COL_S = 0, COL_DP = 128, COL_DS = 256, COL_DQ = 384;  // dS: two 64-column buffers
   static constexpr int TMEM_COLS = 512;
 };
@@ -59,6 +60,7 @@ struct QCfg {
 struct DqTcParams {
   CUtensorMap tq, tk, tv, tdo;
   FaBwdArgs a;
+  StatusRef status;
 };
 
 template <typename T>
@@ -72,17 +74,6 @@ struct QFmt<__nv_bfloat16> {
   static constexpr int kIdesc = 1;
 };
 
-#ifdef FA_BWD_TIMERS
-__device__ unsigned long long g_dq_t[32];
-#define TMR(i) do { long long t_ = clock64(); tm[i] += t_ - tprev; tprev = t_; } while (0)
-__device__ long long g_trace[512];
-#define TRC(ev) do { if (trace_on && j >= 4 && j < 8) g_trace[(j - 4) * 16 + (ev)] = clock64(); } while (0)
-#define TRW(ev) do { if (trace_w && j >= 4 && j < 8) g_trace[64 + warp * 32 + (j - 4) * 8 + (ev)] = clock64(); } while (0)
-#else
-#define TMR(i) do {} while (0)
-#define TRC(ev) do {} while (0)
-#define TRW(ev) do {} while (0)
-#endif
 
 template <typename T, int DH>
 __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_constant__ DqTcParams P) {
@@ -105,9 +96,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
                  bar_dpread = bar0 + 8 * (kB0 + 6);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + C::OFF_BAR + C::NBAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_BAR + C::NBAR * 8 + 4);
-#ifdef FA_BWD_TIMERS
-  volatile long long* t_mark = reinterpret_cast<volatile long long*>(smem + C::OFF_BAR + C::NBAR * 8 + 8);
-#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hq = blockIdx.y, b = blockIdx.z;
@@ -123,11 +111,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
   const int iters = n_hi - n_lo;
 
   if (threadIdx.x == 0) {
-    *abort_flag = g_status;
-    if (s_base & 1023u) {  // the swizzled tiles need a 1024-byte aligned base
-      *abort_flag = W_Q_ALIGN;
-      atomicCAS(&g_status, 0, (int)W_Q_ALIGN);
-    }
+    abort_init(abort_flag, P.status);
+    if (s_base & 1023u) abort_raise(abort_flag, W_Q_ALIGN);  // the swizzled tiles need a 1024-byte aligned base
     for (int s = 0; s < NSK; ++s) {
       mbar_init(bar_k_full(s), 1);
       mbar_init(bar_k_empty(s), 1);
@@ -166,10 +151,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tdP = tmem + lane_off + C::COL_DP + w * 64;
     bool ok = (*abort_flag == 0);  // with iters == 0 the loop is skipped and the epilogue writes zeros
-#ifdef FA_BWD_TIMERS
-    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0;
-    const bool trace_w = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
-#endif
     // per-row statistics of the forward pass; +inf LSE (rows past the end or without keys) gives P = 0
     float lse2 = INFINITY, dsum = 0.f;
     if (qrow < si.sq) {
@@ -180,9 +161,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
     int k_lo = 0, k_hi = si.sk - 1;
     if (a.window_right >= 0) k_hi = min(k_hi, qrow + si.shift + a.window_right);
     if (a.window_left >= 0) k_lo = max(k_lo, qrow + si.shift - a.window_left);
-#ifdef FA_BWD_TIMERS
-    long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
-#endif
     for (int j = 0; j < iters && ok; ++j) {
       const int n0 = (n_lo + j) * kB;
       const uint32_t tS = tmem + lane_off + C::COL_S + w * 64;
@@ -192,12 +170,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
       // ---- P = exp2(S * scale - LSE), 64 key columns per thread, kept in registers
       ok = mbar_wait(bar_s, j & 1, W_Q_S, abort_flag);
       if (!ok) break;
-      TMR(0);
-      TRC(0);
-      TRW(0);
-#ifdef FA_BWD_TIMERS
-      if (j > 0) tm[4] += clock64() - *t_mark;
-#endif
       tc_fence_after();
       float p[64];
       {
@@ -208,9 +180,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_sread);  // S(j) is in registers: S(j+1) may overwrite it
-        TMR(5);
-        TRC(1);
-        TRW(1);
 #pragma unroll
         for (int c = 0; c < 64; ++c)
           p[c] = ex2(fmaf(__uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]), scale_log2, -lse2));
@@ -221,11 +190,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
         for (int c = 0; c < 64; ++c) p[c] = (c >= c_lo && c <= c_hi) ? p[c] : 0.f;
       }
       // ---- dS = P o (dP - D), 16-bit, into this block's dS buffer
-      TMR(1);
       ok = mbar_wait(bar_dp, j & 1, W_Q_DP, abort_flag);
       if (!ok) break;
-      TMR(2);
-      TRC(2);
       tc_fence_after();
       {
         uint32_t d0[32], d1[32], pk[32];
@@ -235,7 +201,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_dpread);  // dP(j) is in registers: dP(j+1) may overwrite it
-        TRC(3);
 #pragma unroll
         for (int c = 0; c < 64; c += 2) {
           const float x0 = p[c] * (__uint_as_float(c < 32 ? d0[c & 31] : d1[c & 31]) - dsum);
@@ -253,16 +218,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_ds);
-      TMR(3);
-      TRC(4);
-      TRW(2);
     }
-#ifdef FA_BWD_TIMERS
-    if (warp == 0 && lane == 0) {
-      for (int i = 0; i < 6; ++i) atomicAdd(&g_dq_t[i], (unsigned long long)tm[i]);
-      atomicAdd(&g_dq_t[7], (unsigned long long)iters);
-    }
-#endif
     // ---- epilogue: dQ * softmax_scale
     if (ok && iters > 0) ok = mbar_wait(bar_done, 0, W_Q_DONE, abort_flag);
     tc_fence_after();
@@ -312,35 +268,18 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
           tma_load_4d(sDO + c * kChunkBytes, &P.tdo, bar_qdo, c * 64, (int)si.q_row0 + m0, hq, qb);
         }
         bool ok = true;
-#ifdef FA_BWD_TIMERS
-        long long tm[6] = {0, 0, 0, 0, 0, 0}, tprev = clock64();
-#endif
         for (int j = 0; j < iters && ok; ++j) {
           const int ks = j % NSK, vs = j % NSV;
           const int row = (int)si.k_row0 + (n_lo + j) * kB;
-          TMR(3);
           ok = mbar_wait(bar_k_empty(ks), ((j / NSK) & 1) ^ 1, W_Q_KV_EMPTY, abort_flag);
           if (!ok) break;
-          TMR(0);
           mbar_expect_tx(bar_k_full(ks), C::TILE_BYTES);
           for (int c = 0; c < C::NCHUNK; ++c) tma_load_4d(sK(ks) + c * kChunkBytes, &P.tk, bar_k_full(ks), c * 64, row, hk, kb);
-          TMR(1);
           ok = mbar_wait(bar_v_empty(vs), ((j / NSV) & 1) ^ 1, W_Q_KV_EMPTY, abort_flag);
           if (!ok) break;
-          TMR(2);
           mbar_expect_tx(bar_v_full(vs), C::TILE_BYTES);
           for (int c = 0; c < C::NCHUNK; ++c) tma_load_4d(sV(vs) + c * kChunkBytes, &P.tv, bar_v_full(vs), c * 64, row, hk, kb);
-#ifdef FA_BWD_TIMERS
-          TMR(3);
-          mbar_wait(bar_k_full(ks), (j / NSK) & 1, W_Q_KV_FULL, abort_flag);
-          { long long t_ = clock64(); tm[4] += t_ - tprev; tprev = t_; }
-          mbar_wait(bar_v_full(vs), (j / NSV) & 1, W_Q_KV_FULL, abort_flag);
-          { long long t_ = clock64(); tm[5] += t_ - tprev; tprev = t_; }
-#endif
         }
-#ifdef FA_BWD_TIMERS
-        for (int i = 0; i < 6; ++i) atomicAdd(&g_dq_t[16 + i], (unsigned long long)tm[i]);
-#endif
       }
     } else if (warp == kWarpMma || warp == kWarpMmaDq) {
       // -------------------------------------------------------------- MMA issuer
@@ -416,21 +355,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
   if (warp == kWarpTmem) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
-#ifdef FA_BWD_TIMERS
-}  // namespace
-}  // namespace fa
-extern "C" void fa_bwd_dq_timers(unsigned long long* out, int reset) {
-  cudaMemcpyFromSymbol(out, fa::g_dq_t, sizeof(unsigned long long) * 32);
-  if (reset == 2) cudaMemcpyFromSymbol(out, fa::g_trace, sizeof(long long) * 64);
-  if (reset == 3) cudaMemcpyFromSymbol(out, fa::g_trace, sizeof(long long) * 320);
-  if (reset) {
-    unsigned long long z[32] = {};
-    cudaMemcpyToSymbol(fa::g_dq_t, z, sizeof(z));
-  }
-}
-namespace fa {
-namespace {
-#endif
 
 template <typename T, int DH>
 int launch_bwd_dq_tc(const FaBwdArgs& a, cudaStream_t st) {
@@ -445,15 +369,9 @@ int launch_bwd_dq_tc(const FaBwdArgs& a, cudaStream_t st) {
   if (make_tmap_4d(&P.tk, a.k, a.dtype, k_rows, a.heads_k, nb, a.head_dim, kB)) return 1;
   if (make_tmap_4d(&P.tv, a.v, a.dtype, k_rows, a.heads_k, nb, a.head_dim, kB)) return 1;
   auto kern = bwd_dq_tc_kernel<T, DH>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) {
-      fa_host::set_error("bwd_dq_tc_kernel: cannot reserve %d bytes of shared memory", C::SMEM_BYTES);
-      cudaGetLastError();
-      return 2;
-    }
-    attr_set = true;
-  }
+  P.status = status_ref(true);
+  static fa_host::DeviceOnce once;
+  if (int rc = fa_host::raise_smem_limit(once, reinterpret_cast<const void*>(kern), C::SMEM_BYTES, "bwd_dq_tc_kernel")) return rc;
   dim3 grid((a.seqlen_q + kB - 1) / kB, a.heads, a.batch);
   kern<<<grid, kThreads, C::SMEM_BYTES, st>>>(P);
   return fa_host::check_launch("bwd_dq_tc_kernel");
@@ -465,17 +383,6 @@ int bwd_dq_tc_main(const FaBwdArgs& a, cudaStream_t st) {
   const bool bf = a.dtype == FA_DTYPE_BF16;
   if (a.head_dim <= 64) return bf ? launch_bwd_dq_tc<__nv_bfloat16, 64>(a, st) : launch_bwd_dq_tc<__half, 64>(a, st);
   return bf ? launch_bwd_dq_tc<__nv_bfloat16, 128>(a, st) : launch_bwd_dq_tc<__half, 128>(a, st);
-}
-
-int bwd_dq_tc_status(bool clear) {
-  int v = 0;
-  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-  if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
-  if (clear && v) {
-    int z = 0;
-    cudaMemcpyToSymbol(g_status, &z, sizeof(int));
-  }
-  return v;
 }
 
 }  // namespace fa

@@ -23,7 +23,6 @@
 // Warps: 0-7 compute (warpgroup w handles query columns [64w, 64w+64) of the block; in the
 // epilogue, head-dim columns [D/2*w, ...)), 8 = TMA producer, 9 = MMA issuer, 10 = loader of the
 // per-row LSE / D vectors and TMEM owner, 11 idle (setmaxnreg is a warpgroup-wide instruction).
-// #define FA_BWD_TIMERS 1  // per-phase cycle counters, read through fa_bwd_timers / fa_bwd_dq_timers
 #include <cstdlib>
 
 #include "../fa_common.cuh"
@@ -33,6 +32,8 @@
 namespace fa {
 
 using namespace ptx;
+
+StatusRef status_ref(bool may_allocate);
 
 namespace {
 
@@ -59,7 +60,7 @@ struct BCfg {
   static constexpr int OFF_STATS = OFF_DO + NSO * TILE_BYTES;  // 2 slots x (128 lse2, 128 dsum) fp32
   static constexpr int OFF_BAR = OFF_STATS + 2 * 1024;
   static constexpr int NBAR = 24;
-  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16;
+  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 32;
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + DH;
   static constexpr int TMEM_COLS = 512;
 };
@@ -67,6 +68,7 @@ struct BCfg {
 struct BwdTcParams {
   CUtensorMap tq, tk, tv, tdo;
   FaBwdArgs a;
+  StatusRef status;
 };
 
 template <typename T>
@@ -80,12 +82,6 @@ struct BFmt<__nv_bfloat16> {
   static constexpr int kIdesc = 1;
 };
 
-#ifdef FA_BWD_TIMERS
-__device__ unsigned long long g_bwd_t[32];
-#define TMR(i) do { long long t_ = clock64(); tm[i] += t_ - tprev; tprev = t_; } while (0)
-#else
-#define TMR(i) do {} while (0)
-#endif
 
 template <typename T, int DH>
 __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_constant__ BwdTcParams P) {
@@ -124,11 +120,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
   const int iters = nmb * group;
 
   if (threadIdx.x == 0) {
-    *abort_flag = g_status;
-    if (s_base & 1023u) {  // the swizzled tiles need a 1024-byte aligned base
-      *abort_flag = W_B_ALIGN;
-      atomicCAS(&g_status, 0, (int)W_B_ALIGN);
-    }
+    abort_init(abort_flag, P.status);
+    if (s_base & 1023u) abort_raise(abort_flag, W_B_ALIGN);  // the swizzled tiles need a 1024-byte aligned base
     mbar_init(bar_kv, 1);
     for (int s = 0; s < NSQ; ++s) {
       mbar_init(bar_q_full(s), 1);
@@ -180,9 +173,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_off + C::COL_S, tdP = tmem + lane_off + C::COL_DP;
     bool ok = (*abort_flag == 0);  // with iters == 0 the loop is skipped and the epilogue writes zeros
-#ifdef FA_BWD_TIMERS
-    long long tm[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tprev = clock64();
-#endif
     Walk wk = walk0;
     for (int it = 0; it < iters && ok; ++it, wk.next()) {
       const int slot = it & 1, par = (it >> 1) & 1;
@@ -196,15 +186,12 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
                              (a.window_right >= 0 && n0 + kB - 1 > m0 + si.shift + a.window_right) ||
                              (a.window_left >= 0 && n0 < m0 + kB - 1 + si.shift - a.window_left);
       // ---- P^T = exp2(S^T * scale - LSE), 64 query columns per thread, into TMEM as the A operand of dV
-      TMR(5);
       ok = mbar_wait(bar_s, it & 1, W_B_S, abort_flag);
       if (!ok) break;
-      TMR(1);
       const float* lse2 = sStats + slot * 256 + w * 64;
       const float* dsum = sStats + slot * 256 + 128 + w * 64;
       ok = mbar_wait(bar_st_full(slot), par, W_B_STATS_FULL, abort_flag);
       if (!ok) break;
-      TMR(0);
       tc_fence_after();
       float p[64];
       {
@@ -233,12 +220,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
           p[c] = (cc >= c_lo && cc <= c_hi) ? p[c] : 0.f;
         }
       }
-      TMR(2);
       // ---- dP^T(it) into registers, then P^T (16-bit) over the first half of this warpgroup's dP^T
       //      columns, where it is the A operand of dV
       ok = mbar_wait(bar_dp, it & 1, W_B_DP, abort_flag);
       if (!ok) break;
-      TMR(3);
       tc_fence_after();
       uint32_t d0[32], d1[32];
       tmem_ld32(tdP + w * 64, d0);
@@ -279,14 +264,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
         mbar_arrive(bar_st_empty(slot));
         mbar_arrive(bar_ds);
       }
-      TMR(4);
     }
-#ifdef FA_BWD_TIMERS
-    if (warp == 0 && lane == 0) {
-      for (int i = 0; i < 6; ++i) atomicAdd(&g_bwd_t[i], (unsigned long long)tm[i]);
-      atomicAdd(&g_bwd_t[7], (unsigned long long)iters);
-    }
-#endif
     // every MMA of the CTA has completed once the last block's Q slot has been released
     if (ok && iters > 0) ok = mbar_wait(bar_q_empty((iters - 1) % NSQ), ((iters - 1) / NSQ) & 1, W_B_QDO_EMPTY, abort_flag);
     tc_fence_after();
@@ -481,10 +459,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
             }
           }
         }
-#ifdef FA_BWD_TIMERS
-        for (int i = 0; i < 8; ++i) atomicAdd(&g_bwd_t[8 + i], (unsigned long long)tm[i]);
-        atomicAdd(&g_bwd_t[16], (unsigned long long)iters);
-#endif
       }
     }
   }
@@ -502,19 +476,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
   if (warp == kWarpStats) tmem_dealloc(tmem, C::TMEM_COLS);
 }
 
-#ifdef FA_BWD_TIMERS
-}  // namespace
-}  // namespace fa
-extern "C" void fa_bwd_timers(unsigned long long* out, int reset) {
-  cudaMemcpyFromSymbol(out, fa::g_bwd_t, sizeof(unsigned long long) * 32);
-  if (reset) {
-    unsigned long long z[32] = {};
-    cudaMemcpyToSymbol(fa::g_bwd_t, z, sizeof(z));
-  }
-}
-namespace fa {
-namespace {
-#endif
 
 template <typename T, int DH>
 int launch_bwd_tc(const FaBwdArgs& a, cudaStream_t st) {
@@ -529,15 +490,9 @@ int launch_bwd_tc(const FaBwdArgs& a, cudaStream_t st) {
   if (make_tmap_4d(&P.tk, a.k, a.dtype, k_rows, a.heads_k, nb, a.head_dim, kB)) return 1;
   if (make_tmap_4d(&P.tv, a.v, a.dtype, k_rows, a.heads_k, nb, a.head_dim, kB)) return 1;
   auto kern = bwd_tc_kernel<T, DH>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) {
-      fa_host::set_error("bwd_tc_kernel: cannot reserve %d bytes of shared memory", C::SMEM_BYTES);
-      cudaGetLastError();
-      return 2;
-    }
-    attr_set = true;
-  }
+  P.status = status_ref(true);
+  static fa_host::DeviceOnce once;
+  if (int rc = fa_host::raise_smem_limit(once, reinterpret_cast<const void*>(kern), C::SMEM_BYTES, "bwd_tc_kernel")) return rc;
   dim3 grid((a.seqlen_k + kB - 1) / kB, a.heads_k, a.batch);
   kern<<<grid, kThreads, C::SMEM_BYTES, st>>>(P);
   return fa_host::check_launch("bwd_tc_kernel");
@@ -561,17 +516,6 @@ int bwd_tc_main(const FaBwdArgs& a, cudaStream_t st) {
   const bool bf = a.dtype == FA_DTYPE_BF16;
   if (a.head_dim <= 64) return bf ? launch_bwd_tc<__nv_bfloat16, 64>(a, st) : launch_bwd_tc<__half, 64>(a, st);
   return bf ? launch_bwd_tc<__nv_bfloat16, 128>(a, st) : launch_bwd_tc<__half, 128>(a, st);
-}
-
-int bwd_tc_status(bool clear) {
-  int v = 0;
-  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-  if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
-  if (clear && v) {
-    int z = 0;
-    cudaMemcpyToSymbol(g_status, &z, sizeof(int));
-  }
-  return v;
 }
 
 }  // namespace fa

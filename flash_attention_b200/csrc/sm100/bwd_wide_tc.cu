@@ -26,6 +26,8 @@ namespace fa {
 
 using namespace ptx;
 
+StatusRef status_ref(bool may_allocate);
+
 namespace {
 
 constexpr int kR = 128;                  // stationary rows per CTA
@@ -57,7 +59,7 @@ struct WCfg {
   static constexpr int STATS_BYTES = PASS == PASS_DQ ? 0 : 8 * 64 * 4;
   static constexpr int OFF_BAR = OFF_STATS + STATS_BYTES;
   static constexpr int NBAR = 2 * NS1 + 2 * NS2 + 8;
-  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16;
+  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 32;
   static constexpr int COL_X1 = 0, COL_X2 = 64, COL_W = 128, COL_OUT = 256;  // W: two 32-column buffers
   static constexpr int TMEM_COLS = 512;
   static_assert(SMEM_BYTES <= 232448, "shared memory of one CTA");
@@ -66,6 +68,7 @@ struct WCfg {
 struct WParams {
   CUtensorMap ta1, ta2, tb1, tb2;  // stationary tiles (128-row boxes), streamed tiles (64-row boxes)
   FaBwdArgs a;
+  StatusRef status;
 };
 
 template <typename T>
@@ -136,11 +139,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_wide_tc_kernel(const __grid_c
   }
 
   if (threadIdx.x == 0) {
-    *abort_flag = g_status;
-    if (s_base & 1023u) {  // the swizzled tiles need a 1024-byte aligned base
-      *abort_flag = W_W_ALIGN;
-      atomicCAS(&g_status, 0, (int)W_W_ALIGN);
-    }
+    abort_init(abort_flag, P.status);
+    if (s_base & 1023u) abort_raise(abort_flag, W_W_ALIGN);  // the swizzled tiles need a 1024-byte aligned base
     for (int s = 0; s < NS1; ++s) {
       mbar_init(bar_b1_full(s), 1);
       mbar_init(bar_b1_empty(s), 1);
@@ -545,15 +545,9 @@ int launch_wide(const FaBwdArgs& a, cudaStream_t st) {
     P.ta1 = tk, P.ta2 = tv, P.tb1 = tq, P.tb2 = tdo;
   }
   auto kern = bwd_wide_tc_kernel<T, PASS>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) {
-      fa_host::set_error("bwd_wide_tc_kernel: cannot reserve %d bytes of shared memory", C::SMEM_BYTES);
-      cudaGetLastError();
-      return 2;
-    }
-    attr_set = true;
-  }
+  P.status = status_ref(true);
+  static fa_host::DeviceOnce once;
+  if (int rc = fa_host::raise_smem_limit(once, reinterpret_cast<const void*>(kern), C::SMEM_BYTES, "bwd_wide_tc_kernel")) return rc;
   dim3 grid(((PASS == PASS_DQ ? a.seqlen_q : a.seqlen_k) + kR - 1) / kR, PASS == PASS_DQ ? a.heads : a.heads_k, a.batch);
   kern<<<grid, kThreads, C::SMEM_BYTES, st>>>(P);
   return fa_host::check_launch("bwd_wide_tc_kernel");
@@ -572,17 +566,6 @@ int run_wide(const FaBwdArgs& a, cudaStream_t st) {
 // dV, dK and dQ of a backward pass with 128 < head_dim <= 256 (softmax_d must hold rowsum(dO o O)).
 int bwd_wide_tc_main(const FaBwdArgs& a, cudaStream_t st) {
   return a.dtype == FA_DTYPE_BF16 ? run_wide<__nv_bfloat16>(a, st) : run_wide<__half>(a, st);
-}
-
-int bwd_wide_tc_status(bool clear) {
-  int v = 0;
-  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-  if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
-  if (clear && v) {
-    int z = 0;
-    cudaMemcpyToSymbol(g_status, &z, sizeof(int));
-  }
-  return v;
 }
 
 }  // namespace fa

@@ -24,6 +24,8 @@ namespace fa {
 
 using namespace ptx;
 
+StatusRef status_ref(bool may_allocate);
+
 namespace {
 
 constexpr int kTileKeys = 64;
@@ -38,6 +40,7 @@ struct DecodeParams {
   FaKvcacheArgs a;
   int num_splits;
   int keys_per_split;  // multiple of kTileKeys
+  StatusRef status;
 };
 
 template <int D>
@@ -48,7 +51,7 @@ struct DCfg {
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
   static constexpr int Q_LD = D + 8;
   static constexpr int Q_BYTES = kMaxRows * Q_LD * 2;
-  static constexpr int SMEM_BYTES = kStages * STAGE_BYTES + Q_BYTES + (2 * kStages + 1) * 8 + 16 + 1024;
+  static constexpr int SMEM_BYTES = kStages * STAGE_BYTES + Q_BYTES + (2 * kStages + 1) * 8 + 32 + 1024;
 };
 
 // address of (row, 16-byte chunk c16 of the 128-byte row) inside one swizzled TMA box
@@ -132,7 +135,7 @@ __global__ void __launch_bounds__(160, 2) decode_kernel(const __grid_constant__ 
   auto bar_full = [&](int s) { return bar0 + 8 * s; };
   auto bar_empty = [&](int s) { return bar0 + 8 * (kStages + s); };
   const uint32_t bar_rdv = bar0 + 8 * 2 * kStages;  // rendezvous of the four consumer warps
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kStages * C::STAGE_BYTES + C::Q_BYTES + (2 * kStages + 1) * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kStages * C::STAGE_BYTES + C::Q_BYTES + (2 * kStages + 1) * 8 + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -170,7 +173,7 @@ __global__ void __launch_bounds__(160, 2) decode_kernel(const __grid_constant__ 
   const int ntiles = (key_hi - key_lo + kTileKeys - 1) / kTileKeys;
 
   if (tid == 0) {
-    *abort_flag = g_status;
+    abort_init(abort_flag, P.status);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar_full(s), 1);
       mbar_init(bar_empty(s), 4);
@@ -407,7 +410,7 @@ __global__ void __launch_bounds__(160, 2) decode_kernel(const __grid_constant__ 
 }
 
 template <typename T, int D>
-int launch_decode(const FaKvcacheArgs& a, int num_splits, int keys_per_split, cudaStream_t st) {
+int launch_decode(const FaKvcacheArgs& a, int num_splits, int keys_per_split, cudaStream_t st, bool may_allocate) {
   using C = DCfg<D>;
   DecodeParams P;
   P.a = a;
@@ -416,15 +419,9 @@ int launch_decode(const FaKvcacheArgs& a, int num_splits, int keys_per_split, cu
   if (make_tmap_4d(&P.tk, a.kcache, a.dtype, a.seqlen_cache, a.heads_k, a.batch_cache, a.head_dim, kTileKeys)) return 1;
   if (make_tmap_4d(&P.tv, a.vcache, a.dtype, a.seqlen_cache, a.heads_k, a.batch_cache, a.head_dim, kTileKeys)) return 1;
   auto kern = decode_kernel<T, D>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) {
-      fa_host::set_error("decode_kernel: cannot reserve %d bytes of shared memory", C::SMEM_BYTES);
-      cudaGetLastError();
-      return 2;
-    }
-    attr_set = true;
-  }
+  P.status = status_ref(may_allocate);
+  static fa_host::DeviceOnce once;
+  if (int rc = fa_host::raise_smem_limit(once, reinterpret_cast<const void*>(kern), C::SMEM_BYTES, "decode_kernel")) return rc;
   dim3 grid(num_splits, a.heads_k, a.batch);
   kern<<<grid, 160, C::SMEM_BYTES, st>>>(P);
   return fa_host::check_launch("decode_kernel");
@@ -474,14 +471,14 @@ int decode_plan(const FaKvcacheArgs& a, int num_sms) {
   return splits;
 }
 
-int decode_run(const FaKvcacheArgs& a, int num_splits, cudaStream_t st) {
+int decode_run(const FaKvcacheArgs& a, int num_splits, cudaStream_t st, bool may_allocate) {
   const int kps = keys_per_split_of(a, num_splits);
   const bool bf = a.dtype == FA_DTYPE_BF16;
   int rc;
   if (a.head_dim == 64)
-    rc = bf ? launch_decode<__nv_bfloat16, 64>(a, num_splits, kps, st) : launch_decode<__half, 64>(a, num_splits, kps, st);
+    rc = bf ? launch_decode<__nv_bfloat16, 64>(a, num_splits, kps, st, may_allocate) : launch_decode<__half, 64>(a, num_splits, kps, st, may_allocate);
   else
-    rc = bf ? launch_decode<__nv_bfloat16, 128>(a, num_splits, kps, st) : launch_decode<__half, 128>(a, num_splits, kps, st);
+    rc = bf ? launch_decode<__nv_bfloat16, 128>(a, num_splits, kps, st, may_allocate) : launch_decode<__half, 128>(a, num_splits, kps, st, may_allocate);
   if (rc) return rc;
   if (num_splits > 1)
     return combine(a.out_accum, a.lse_accum, a.out, a.softmax_lse, a.seqlen_q, num_splits, a.batch, a.heads, a.seqlen_q,
@@ -496,6 +493,24 @@ constexpr size_t kNoAllocScratchBytes = 24u << 20;  // 24 MiB
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 size_t decode_noalloc_capacity() { return kNoAllocScratchBytes; }
+
+static size_t noalloc_bytes_needed(const FaKvcacheArgs& a, int num_splits) {
+  const size_t rows = (size_t)a.batch * a.heads * a.seqlen_q;
+  const size_t lse_bytes = (rows * num_splits * sizeof(float) + 255) & ~size_t(255);
+  return lse_bytes + rows * num_splits * (size_t)a.head_dim * sizeof(float);
+}
+
+// Largest split count <= `num_splits` (in the rounding of decode_plan) whose partials fit the
+// built-in buffer; 1 always fits (a single split writes no partials).
+int decode_noalloc_fit(const FaKvcacheArgs& a, int num_splits) {
+  const int tiles = (a.seqlen_cache + kTileKeys - 1) / kTileKeys;
+  while (num_splits > 1 && noalloc_bytes_needed(a, num_splits) > kNoAllocScratchBytes) {
+    --num_splits;
+    const int per = (tiles + num_splits - 1) / num_splits;
+    num_splits = (tiles + per - 1) / per;
+  }
+  return num_splits;
+}
 
 // In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address; the
 // address on the current device is looked up once per device and cached.
@@ -541,18 +556,7 @@ int decode_run_noalloc(const FaKvcacheArgs& a, int num_splits, cudaStream_t st) 
     b.lse_accum = reinterpret_cast<float*>(base);
     b.out_accum = reinterpret_cast<float*>(base + lse_bytes);
   }
-  return decode_run(b, num_splits, st);
-}
-
-int decode_status(bool clear) {
-  int v = 0;
-  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-  if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
-  if (clear && v) {
-    int z = 0;
-    cudaMemcpyToSymbol(g_status, &z, sizeof(int));
-  }
-  return v;
+  return decode_run(b, num_splits, st, /*may_allocate=*/false);
 }
 
 }  // namespace fa

@@ -28,6 +28,8 @@ namespace fa {
 
 using namespace ptx;
 
+StatusRef status_ref(bool may_allocate);
+
 namespace {
 
 constexpr int kBM = 128;  // rows per query tile
@@ -47,7 +49,7 @@ struct Cfg {
   static constexpr int STAGES = DH > 128 ? 2 : (DH == 128 ? 4 : 8);
   static constexpr int SMEM_TILES = (NT + STAGES) * TILE_BYTES;
   static constexpr int NBAR = 2 + 2 * STAGES + 6;
-  static constexpr int SMEM_BYTES = SMEM_TILES + NBAR * 8 + 16 + 1024;  // + barriers, tmem ptr/abort, align slack
+  static constexpr int SMEM_BYTES = SMEM_TILES + NBAR * 8 + 32 + 1024;  // + barriers, tmem ptr / abort block, align slack
   static constexpr int TMEM_COLS = 512;
   static constexpr int COL_S0 = 0, COL_S1 = 128, COL_O0 = 256, COL_O1 = 256 + DH;
 };
@@ -55,6 +57,7 @@ struct Cfg {
 struct FwdTcParams {
   CUtensorMap tq, tk, tv;
   FaFwdArgs a;
+  StatusRef status;
 };
 
 template <typename T>
@@ -123,7 +126,7 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
   const int nblk = J_hi - J_lo;  // may be 0
 
   if (threadIdx.x == 0) {
-    *abort_flag = g_status;  // a failed earlier launch makes every later CTA bail out at its first wait
+    abort_init(abort_flag, P.status);
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_qfull(t), 1);
       mbar_init(bar_sfull(t), 1);
@@ -466,16 +469,10 @@ int launch_fwd_tc(const FaFwdArgs& a, cudaStream_t st) {
   if (make_tmap_4d(&P.tq, a.q, a.dtype, q_rows, a.heads, nb, a.head_dim, kBM)) return 1;
   if (make_tmap_4d(&P.tk, a.k, a.dtype, k_rows, a.heads_k, nb, a.head_dim, kBN)) return 1;
   if (make_tmap_4d(&P.tv, a.v, a.dtype, k_rows, a.heads_k, nb, a.head_dim, kBN)) return 1;
+  P.status = status_ref(true);
   auto kern = fwd_tc_kernel<T, DH>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) {
-      fa_host::set_error("fwd_tc_kernel: cannot reserve %d bytes of shared memory: %s", C::SMEM_BYTES,
-                         cudaGetErrorString(cudaGetLastError()));
-      return 2;
-    }
-    attr_set = true;
-  }
+  static fa_host::DeviceOnce once;
+  if (int rc = fa_host::raise_smem_limit(once, reinterpret_cast<const void*>(kern), C::SMEM_BYTES, "fwd_tc_kernel")) return rc;
   dim3 grid((a.seqlen_q + C::NT * kBM - 1) / (C::NT * kBM), a.heads, a.batch);
   kern<<<grid, 384, C::SMEM_BYTES, st>>>(P);
   return fa_host::check_launch("fwd_tc_kernel");
@@ -499,17 +496,6 @@ int fwd_tc(const FaFwdArgs& a, cudaStream_t st) {
   if (a.head_dim <= 64) return bf ? launch_fwd_tc<__nv_bfloat16, 64>(a, st) : launch_fwd_tc<__half, 64>(a, st);
   if (a.head_dim <= 128) return bf ? launch_fwd_tc<__nv_bfloat16, 128>(a, st) : launch_fwd_tc<__half, 128>(a, st);
   return bf ? launch_fwd_tc<__nv_bfloat16, 256>(a, st) : launch_fwd_tc<__half, 256>(a, st);
-}
-
-int fwd_tc_status(bool clear) {
-  int v = 0;
-  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-  if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
-  if (clear && v) {
-    int z = 0;
-    cudaMemcpyToSymbol(g_status, &z, sizeof(int));
-  }
-  return v;
 }
 
 }  // namespace fa

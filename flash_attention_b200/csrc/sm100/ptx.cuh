@@ -9,12 +9,42 @@
 namespace fa {
 namespace ptx {
 
-// Every wait in the tensor-core kernels is bounded: a wait that has not completed after
-// kWaitCycles SM cycles gives up, records `code` in the status word and the kernel winds down
-// (all other waits then fail fast), so a protocol bug shows up as an error code, not as a hang.
+// Every wait in the tensor-core kernels is bounded: a wait that has not completed after `limit` SM
+// cycles (kWaitCycles unless a caller says otherwise) gives up, records `code` in the CTA's abort
+// flag and in the device status word, and the kernel winds down (all other waits then fail fast),
+// so a protocol bug shows up as an error code, not as a hang.
 constexpr long long kWaitCycles = 3000000000ll;  // ~1.5 s at 2 GHz
 
-static __device__ int g_status = 0;  // 0 = ok; otherwise code of the first wait that gave up
+// Where a kernel reports a wait that gave up: one word in device memory (the library's status
+// word, shared by all its kernels) and, when the host has one, its mirror in mapped host memory,
+// which the entry points read without synchronising.  Passed to every kernel by value.
+struct StatusRef {
+  int* dev;
+  int* host;  // may be null
+};
+
+// Shared-memory block of every kernel that waits: [tmem address][abort flag][StatusRef], 24 bytes,
+// 8-byte aligned.  Kernels hold a pointer to the abort flag; the StatusRef sits right behind it.
+constexpr int kAbortBlockBytes = 24;
+__device__ __forceinline__ void abort_publish(volatile int* abort_flag, int code) {
+  int* dev = *reinterpret_cast<int* volatile*>(const_cast<int*>(abort_flag) + 1);
+  int* host = *reinterpret_cast<int* volatile*>(const_cast<int*>(abort_flag) + 3);
+  if (dev != nullptr && atomicCAS(dev, 0, code) == 0 && host != nullptr) {
+    *reinterpret_cast<volatile int*>(host) = code;
+    __threadfence_system();
+  }
+}
+// One thread, before the CTA's first barrier: a failed earlier launch makes every later CTA bail
+// out at its first wait (the status word is sticky until the host clears it).
+__device__ __forceinline__ void abort_init(volatile int* abort_flag, const StatusRef& s) {
+  *reinterpret_cast<int* volatile*>(const_cast<int*>(abort_flag) + 1) = s.dev;
+  *reinterpret_cast<int* volatile*>(const_cast<int*>(abort_flag) + 3) = s.host;
+  *abort_flag = s.dev ? *reinterpret_cast<volatile int*>(s.dev) : 0;
+}
+__device__ __forceinline__ void abort_raise(volatile int* abort_flag, int code) {
+  *abort_flag = code;
+  abort_publish(abort_flag, code);
+}
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -74,7 +104,7 @@ __device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
 }
 // Returns false (and records `code`) when the wait gave up or the kernel is already aborting.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code, volatile int* abort_flag,
-                                          int mode = 0) {
+                                          int mode = 0, long long limit = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t polls = 0;
@@ -87,9 +117,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 63u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) {
-        *abort_flag = code;
-        atomicCAS(&g_status, 0, code);
+      if (clock64() - t0 > limit) {
+        abort_raise(abort_flag, code);
         return false;
       }
     }

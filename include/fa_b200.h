@@ -157,8 +157,11 @@ int fa_fwd_kvcache(const FaKvcacheArgs* args, fa_stream_t stream);
    Limits and rules:
      - only the single-token decode shape (seqlen_q * heads / heads_k <= 16, head_dim 64 or 128, no
        window, at most one new token); anything else is refused with status 1;
-     - num_splits * batch * heads * seqlen_q * (head_dim + 1) * 4 bytes must fit the buffer, else the
-       call is refused with a message saying so (pass a smaller num_splits);
+     - with rows = batch * heads * seqlen_q, the partials of a call with S > 1 splits take
+       round_up(S * rows * 4, 256) + S * rows * head_dim * 4 bytes.  With num_splits = 0 (choose) the
+       library picks the largest split count of its plan that fits the buffer (one split always fits:
+       it writes no partials); an explicit num_splits that does not fit is refused with a message
+       saying so;
      - the first call on each device looks up the buffer's address (with that device current); make
        that first call outside any stream capture;
      - all calls share the one buffer, which keeps whatever the previous call left in it.  Nothing in
@@ -227,9 +230,22 @@ int fa_abi_struct_size(int32_t which);
 const char* fa_last_error(void);
 /* Compile-time facts: "sm_100a", kernel list, build flags. */
 const char* fa_build_info(void);
-/* Device-side status word of the tensor-core kernels: 0 = ok, otherwise the code of the first
-   bounded wait that gave up (the kernels never spin forever).  Synchronises the device. */
+/* Device-side status word of the tensor-core and decode kernels: 0 = ok, otherwise the code of the
+   first bounded wait that gave up (the kernels never spin forever; the reference has no such word,
+   its kernels use unbounded __syncthreads / cp.async waits).  The word is sticky: once set, kernels
+   of later calls wind down without writing their outputs, and fa_fwd / fa_bwd / fa_fwd_kvcache /
+   fa_fwd_kvcache_noalloc return status 3 without launching (they see the word through a mirror in
+   mapped host memory, without synchronising).  fa_device_status() synchronises the current device,
+   returns the word and clears it, after which calls are accepted again. */
 int fa_device_status(void);
+/* Self-tests of the failure path (no counterpart in the reference).  fa_selftest_wait_timeout
+   launches one warp that waits, for at most limit_cycles SM cycles, on a barrier nobody arrives at,
+   and so sets the status word to 99 exactly as a stuck pipeline would; nothing faults or hangs.
+   fa_selftest_device_once replays the per-device "raise the shared-memory limit once" bookkeeping of
+   the kernel launchers on a list of device ordinals (host only): needed[i] = 1 where call i would
+   have configured its device. */
+int fa_selftest_wait_timeout(int64_t limit_cycles, fa_stream_t stream);
+int fa_selftest_device_once(const int32_t* devices, int32_t n, int32_t* needed);
 
 #ifdef __cplusplus
 }

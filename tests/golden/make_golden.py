@@ -118,4 +118,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and not os.environ.get("FLASH_ATTN_REFERENCE_TREE"):
+        sys.exit("usage: make_golden.py /path/to/flash-attention  (or set FLASH_ATTN_REFERENCE_TREE)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["FLASH_ATTN_REFERENCE_TREE"])

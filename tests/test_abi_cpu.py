@@ -125,16 +125,37 @@ def test_shim_raises_runtime_error_like_torch_check():
         ext.fwd(q, q, q, None, 0.0, 1.0, False, -1, -1, False, None)
 
 
-@pytest.mark.skipif(not os.path.exists("/root/reference/flash_attn/flash_attn_interface.py"), reason="reference tree not present")
+def _reference_interface_file():
+    """flash_attn/flash_attn_interface.py of an unmodified FlashAttention v2.3.3: from the tree named by
+    FLASH_ATTN_REFERENCE_TREE, else from the python-only install under baseline/_ref of this repository."""
+    roots = [os.environ.get("FLASH_ATTN_REFERENCE_TREE"), os.path.join(ROOT, "baseline", "_ref")]
+    for r in roots:
+        if r and os.path.exists(os.path.join(r, "flash_attn", "flash_attn_interface.py")):
+            return os.path.join(r, "flash_attn", "flash_attn_interface.py")
+    return None
+
+
+@pytest.mark.skipif(_reference_interface_file() is None, reason="reference tree not present")
 def test_unmodified_reference_interface_binds_to_the_shim():
     # the reference's python API file, loaded as is, must find everything it calls in our module
     import importlib.util
 
     import flash_attn_2_cuda as ext
 
-    spec = importlib.util.spec_from_file_location("ref_iface", "/root/reference/flash_attn/flash_attn_interface.py")
+    spec = importlib.util.spec_from_file_location("ref_iface", _reference_interface_file())
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     assert mod.flash_attn_cuda is ext
     for fn in ("flash_attn_func", "flash_attn_qkvpacked_func", "flash_attn_varlen_func", "flash_attn_with_kvcache"):
         assert callable(getattr(mod, fn))
+
+
+def test_per_device_setup_runs_once_per_device(lib):
+    # the launchers raise a kernel's shared-memory limit once per DEVICE (the attribute is per device):
+    # replay the bookkeeping for a process that alternates between GPUs
+    devs = [0, 0, 1, 0, 1, 2, 63, 63, 64, 64, -1, -1]
+    arr = (ctypes.c_int32 * len(devs))(*devs)
+    out = (ctypes.c_int32 * len(devs))()
+    assert lib.fa_selftest_device_once(arr, len(devs), out) == 0
+    # ordinals outside the 64-entry table are configured on every call rather than never
+    assert list(out) == [1, 0, 1, 0, 0, 1, 1, 0, 1, 1, 1, 1]
