@@ -107,7 +107,7 @@ EXPORTS = (
     "fa_fwd", "fa_bwd", "fa_fwd_kvcache", "fa_fwd_num_splits", "fa_kvcache_plan", "fa_bwd_workspace_bytes",
     "fa_combine", "fa_last_error", "fa_build_info", "fa_device_status", "fa_abi_struct_size",
     "fa_fwd_kvcache_noalloc", "fa_noalloc_scratch_bytes", "fa_merge_partial", "fa_rotary",
-    "fa_selftest_wait_timeout", "fa_selftest_device_once",
+    "fa_selftest_wait_timeout", "fa_selftest_device_once", "fa_last_path",
 )
 
 _lib = None
@@ -147,6 +147,7 @@ def lib():
         L.fa_rotary.restype = C.c_int
         L.fa_last_error.restype = C.c_char_p
         L.fa_build_info.restype = C.c_char_p
+        L.fa_last_path.restype = C.c_char_p
         L.fa_device_status.restype = C.c_int
         L.fa_selftest_wait_timeout.argtypes = [c_i64, c_vp]
         L.fa_selftest_wait_timeout.restype = C.c_int
@@ -163,6 +164,11 @@ def lib():
 
 def last_error():
     return lib().fa_last_error().decode()
+
+
+def last_path():
+    """Kernels launched by this thread's last fa_fwd / fa_bwd / fa_fwd_kvcache call."""
+    return lib().fa_last_path().decode()
 
 
 def check(status, what):

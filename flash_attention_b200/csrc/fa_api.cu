@@ -91,6 +91,9 @@ static int env_flag(const char* name) {
 
 using fa_host::set_error;
 
+// Which kernels the last fa_fwd / fa_bwd / fa_fwd_kvcache call of this thread launched (fa_last_path()).
+static thread_local const char* g_last_path = "";
+
 static int check_tensor(const FaTensor& t, const char* name) {
   FA_REQUIRE(t.ptr != nullptr, "%s: null pointer", name);
   FA_REQUIRE((reinterpret_cast<uintptr_t>(t.ptr) & 15) == 0, "%s: pointer must be 16-byte aligned", name);
@@ -125,6 +128,8 @@ static int refuse_if_device_failed() {
 extern "C" {
 
 const char* fa_last_error(void) { return fa_host::g_err; }
+
+const char* fa_last_path(void) { return g_last_path; }
 
 const char* fa_build_info(void) {
   return "libfa_b200 arch=sm_100a kernels=fwd_tc(tcgen05+TMA),bwd_dkdv_tc(tcgen05+TMA),bwd_dq_tc(tcgen05+TMA),bwd_wide_tc(tcgen05+TMA),decode_splitkv(TMA),"
@@ -216,8 +221,11 @@ int fa_fwd(const FaFwdArgs* a, fa_stream_t stream) {
   }
   if (a->seqlen_q == 0 || a->batch == 0) return 0;
   if (refuse_if_device_failed()) return 3;
-  if (a->num_splits <= 1 && !fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::fwd_tc_eligible(*a))
+  if (a->num_splits <= 1 && !fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::fwd_tc_eligible(*a)) {
+    g_last_path = "fwd_tc";
     return fa::fwd_tc(*a, st);
+  }
+  g_last_path = a->num_splits > 1 ? "fwd_generic+combine" : "fwd_generic";
   int rc = fa::fwd_generic(*a, st);
   if (rc) return rc;
   if (a->num_splits > 1)
@@ -249,6 +257,7 @@ int fa_bwd(const FaBwdArgs* a, fa_stream_t stream) {
   // the tensor-core path writes dq directly (two kernels: dK / dV per key block, dQ per query block)
   int rc = fa::bwd_pre(*a, tc ? 0 : 1, st);
   if (rc) return rc;
+  g_last_path = !tc ? "bwd_generic" : (a->head_dim > 128 ? "bwd_wide_tc" : "bwd_tc+bwd_dq_tc");
   if (tc) {
     if (a->head_dim > 128) return fa::bwd_wide_tc_main(*a, st);  // one pass per output
     rc = fa::bwd_tc_main(*a, st);
@@ -312,7 +321,11 @@ int fa_fwd_kvcache(const FaKvcacheArgs* a, fa_stream_t stream) {
   if (splits > 1) FA_REQUIRE(a->lse_accum && a->out_accum, "split-KV needs lse_accum and out_accum");
   if (a->seqlen_q == 0) return 0;
   if (refuse_if_device_failed()) return 3;
-  if (!fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::decode_eligible(*a)) return fa::decode_run(*a, splits, st);
+  if (!fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::decode_eligible(*a)) {
+    g_last_path = splits > 1 ? "decode+combine" : "decode";
+    return fa::decode_run(*a, splits, st);
+  }
+  g_last_path = splits > 1 ? "kvcache_prep+fwd_generic+combine" : "kvcache_prep+fwd_generic";
 
   // General path: append/rotate in a first launch, then the any-shape forward on the cache.
   const bool causal_or_local = a->window_left >= 0 || a->window_right >= 0;
@@ -374,6 +387,7 @@ int fa_fwd_kvcache_noalloc(const FaKvcacheArgs* a, fa_stream_t stream) {
   if (a->num_splits == 0) splits = fa::decode_noalloc_fit(*a, splits);
   if (a->seqlen_q == 0) return 0;
   if (refuse_if_device_failed()) return 3;
+  g_last_path = splits > 1 ? "decode+combine" : "decode";
   return fa::decode_run_noalloc(*a, splits, st);
 }
 

@@ -11,6 +11,7 @@ workspaces, RNG bookkeeping, the seqlen_q==1 grouped-query reshape — is done h
 There is no fallback path: every function ends in a call into the CUDA library.
 """
 import ctypes
+import os
 
 import torch
 import torch.nn.functional as F
@@ -163,6 +164,8 @@ def fwd(q, k, v, out_, p_dropout, softmax_scale, is_causal, window_size_left, wi
             keep = None
             if p_dropout == 0.0:  # flash_api.cpp:373-389
                 ns = lib().fa_fwd_num_splits(batch, heads, seqlen_q, seqlen_k, d, _sm_count(q.device))
+                if os.environ.get("FA_B200_FWD_SPLITS"):  # test knob: pin the split count (1 = never split)
+                    ns = max(1, min(128, int(os.environ["FA_B200_FWD_SPLITS"])))
                 if ns > 1:
                     lse_acc = torch.empty((ns, batch, heads, seqlen_q), dtype=torch.float32, device=q.device)
                     out_acc = torch.empty((ns, batch, heads, seqlen_q, d), dtype=torch.float32, device=q.device)

@@ -17,17 +17,37 @@ pytestmark = pytest.mark.gpu
 
 if torch.cuda.is_available():
     import flash_attention_b200 as fa
+    from flash_attention_b200 import _lib
 
 
-def _run(q, k, v, do, **kw):
+class one_pass_forward:
+    """Pins the forward to a single pass over the keys (no split-KV), so that a small problem, which the
+    split heuristic would hand to the split path, runs on the kernel that large problems take."""
+
+    def __enter__(self):
+        self.old = os.environ.get("FA_B200_FWD_SPLITS")
+        os.environ["FA_B200_FWD_SPLITS"] = "1"
+
+    def __exit__(self, *a):
+        if self.old is None:
+            del os.environ["FA_B200_FWD_SPLITS"]
+        else:
+            os.environ["FA_B200_FWD_SPLITS"] = self.old
+
+
+def _run(q, k, v, do, fwd_path=None, bwd_path=None, **kw):
     q, k, v = (x.detach().clone().requires_grad_(True) for x in (q, k, v))
     out, lse, _ = fa.flash_attn_func(q, k, v, return_attn_probs=True, **kw)
+    if fwd_path is not None:
+        assert _lib.last_path() == fwd_path, "forward took %r, the case is meant for %r" % (_lib.last_path(), fwd_path)
     dq, dk, dv = torch.autograd.grad(out, (q, k, v), do)
+    if bwd_path is not None:
+        assert _lib.last_path() == bwd_path, "backward took %r, the case is meant for %r" % (_lib.last_path(), bwd_path)
     return out.detach(), lse, dq, dk, dv
 
 
-def _check(q, k, v, do, causal=False, window=(-1, -1), grads=True):
-    out, lse, dq, dk, dv = _run(q, k, v, do, causal=causal, window_size=window)
+def _check(q, k, v, do, causal=False, window=(-1, -1), grads=True, fwd_path=None, bwd_path=None):
+    out, lse, dq, dk, dv = _run(q, k, v, do, causal=causal, window_size=window, fwd_path=fwd_path, bwd_path=bwd_path)
     # The kernels treat a one-sided window as unbounded on the other side (set_params_fprop,
     # csrc/flash_attn/flash_api.cpp:113-114); attention_ref takes the -1 literally, so the oracle
     # is given seqlen_k for the open side.
@@ -58,6 +78,18 @@ def test_mha_head_dims(sq, sk, d, causal, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("d", [32, 40, 59, 64, 80, 96, 111, 128, 160, 192, 224, 256])
+@pytest.mark.parametrize("sq,sk", [(113, 203), (128, 217), (1, 147), (512, 256), (384, 384)])
+def test_mha_head_dims_on_the_tensor_core_kernels(sq, sk, d, causal, dtype):
+    # the lattice above at the same small sizes, but pinned to the kernels that large problems run on:
+    # single-pass tcgen05 forward, tcgen05 backward (two kernels up to head dim 128, three passes above)
+    q, k, v, do = make_qkv(2, sq, sk, 4, 4, d, dtype, seed=d + sq)
+    with one_pass_forward():
+        _check(q, k, v, do, causal=causal, fwd_path="fwd_tc", bwd_path="bwd_wide_tc" if d > 128 else "bwd_tc+bwd_dq_tc")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("local", [False, True])
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("hk", [1, 3, 9])
@@ -75,6 +107,8 @@ def test_gqa_and_windows(sq, sk, d, hk, causal, local, dtype):
 def test_window_edges(sq, sk, window):
     q, k, v, do = make_qkv(1, sq, sk, 2, 2, 128, torch.bfloat16, seed=3)
     _check(q, k, v, do, window=window)
+    with one_pass_forward():
+        _check(q, k, v, do, window=window, fwd_path="fwd_tc", bwd_path="bwd_tc+bwd_dq_tc")
 
 
 def test_qkvpacked_and_kvpacked_match_unpacked():
@@ -159,6 +193,12 @@ def test_deterministic_out_lse_dk_dv():
         assert torch.equal(cur[0], ref[0]) and torch.equal(cur[1], ref[1])
         assert torch.equal(cur[3], ref[3]) and torch.equal(cur[4], ref[4])
         assert (cur[2].float() - ref[2].float()).abs().max().item() <= 2e-2
+    # on the tensor-core kernels nothing is accumulated atomically: dq is bit-identical too
+    with one_pass_forward():
+        ref = _run(q, k, v, do, causal=True, fwd_path="fwd_tc", bwd_path="bwd_tc+bwd_dq_tc")
+        for _ in range(20):
+            cur = _run(q, k, v, do, causal=True)
+            assert all(torch.equal(x, y) for x, y in zip(cur, ref))
 
 
 def test_backward_large_values_do_not_overflow():
