@@ -167,7 +167,7 @@ def last_error():
 
 
 def last_path():
-    """Kernels launched by this thread's last fa_fwd / fa_bwd / fa_fwd_kvcache call."""
+    """Kernels launched by this process's last fa_fwd / fa_bwd / fa_fwd_kvcache call (any thread)."""
     return lib().fa_last_path().decode()
 
 

@@ -91,8 +91,9 @@ static int env_flag(const char* name) {
 
 using fa_host::set_error;
 
-// Which kernels the last fa_fwd / fa_bwd / fa_fwd_kvcache call of this thread launched (fa_last_path()).
-static thread_local const char* g_last_path = "";
+// Which kernels the last fa_fwd / fa_bwd / fa_fwd_kvcache call of this process launched (fa_last_path()).
+// Process-wide on purpose: a backward pass runs on an autograd worker thread, not on the caller's.
+static const char* volatile g_last_path = "";
 
 static int check_tensor(const FaTensor& t, const char* name) {
   FA_REQUIRE(t.ptr != nullptr, "%s: null pointer", name);

@@ -6,7 +6,7 @@
 //   warps 0-3   softmax of tile 0  (one thread per query row; tcgen05.ld 32x32b gives a thread its row)
 //   warps 4-7   softmax of tile 1
 //   warp  8     TMA producer: Q tiles once, then K(j), V(j), K(j+1), ... through a ring of slots
-//   warp  9     MMA issuer: one elected thread issues every tcgen05.mma
+//   warp  9     MMA issuer: the warp stays converged, one elected lane issues every tcgen05.mma
 //   warp  10    owns the TMEM allocation
 // TMEM columns (fp32): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).  P (16-bit) is
 // written over the first 64 columns of its S and fed to the PV MMA as the TMEM A operand.
@@ -329,7 +329,7 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
       }
     } else if (warp == 9) {
       // ---------------------------------------------------------------- MMA issuer
-      if (lane == 0) {
+      {  // the whole warp runs the loop (see mma_ss_w); one elected lane issues
         constexpr uint32_t idesc_s = make_idesc(kBM, kBN, Fmt<T>::kIdesc, 0, 0);
         constexpr uint32_t idesc_o = make_idesc(kBM, DH, Fmt<T>::kIdesc, 0, 1);
         bool ok = true;
@@ -347,17 +347,17 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
 #pragma unroll
           for (int kk = 0; kk < DH / 16; ++kk) {
             const uint32_t off = (uint32_t)(((kk >> 2) * kChunkBytes + (kk & 3) * 32) >> 4);
-            mma_ss(d, dsc(a_lo + off), dsc(b_lo + off), idesc_s, kk > 0);
+            mma_ss_w(d, dsc(a_lo + off), dsc(b_lo + off), idesc_s, kk > 0);
           }
-          tc_commit(bar_sfull(t));
+          tc_commit_w(bar_sfull(t));
         };
         auto issue_pv = [&](int t, int slot, bool first) {
           const uint32_t d = tmem + (t ? C::COL_O1 : C::COL_O0);
           const uint32_t pa = tmem + (t ? C::COL_S1 : C::COL_S0);
           const uint32_t b_lo = oKV + slot * kTile16 + kMn;
 #pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) mma_ts(d, pa + kk * 8, dsc(b_lo + (uint32_t)((kk * 2048) >> 4)), idesc_o, (!first) || kk > 0);
-          tc_commit(bar_ofull(t));
+          for (int kk = 0; kk < kBN / 16; ++kk) mma_ts_w(d, pa + kk * 8, dsc(b_lo + (uint32_t)((kk * 2048) >> 4)), idesc_o, (!first) || kk > 0);
+          tc_commit_w(bar_ofull(t));
         };
         auto in_range = [&](int t, int j) { return j >= lo[t] && j < hi[t]; };
         auto slot_of = [&](int idx) { return idx % C::STAGES; };
@@ -371,7 +371,7 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
             if (ok) {
               tc_fence_after();
               issue_s(0, slot_of(0));
-              tc_commit(bar_empty(slot_of(0)));
+              tc_commit_w(bar_empty(slot_of(0)));
             }
             for (int j = J_lo; j < J_hi && ok; ++j) {
               const int iv = 2 * (j - J_lo) + 1, ik = iv + 1;  // ring indices of V(j) and K(j+1)
@@ -383,10 +383,10 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
               ++p_iter[0];
               tc_fence_after();
               issue_pv(0, slot_of(iv), j == J_lo);
-              tc_commit(bar_empty(slot_of(iv)));
+              tc_commit_w(bar_empty(slot_of(iv)));
               if (more) {
                 issue_s(0, slot_of(ik));
-                tc_commit(bar_empty(slot_of(ik)));
+                tc_commit_w(bar_empty(slot_of(ik)));
               }
             }
           }
@@ -399,7 +399,7 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
             tc_fence_after();
             for (int t = 0; t < 2; ++t)
               if (in_range(t, J_lo)) issue_s(t, slot_of(0));
-            tc_commit(bar_empty(slot_of(0)));
+            tc_commit_w(bar_empty(slot_of(0)));
           }
           // Every barrier is tested one MMA group ahead of its use (see mbar_test): the answers for
           // V(j), K(j+1) and tile 0's P are requested while tile 1's group of the block before is being
@@ -434,9 +434,9 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
                 h_p[0] = mbar_test(bar_pfull(0), p_iter[0] & 1);
               }
               if (pv) issue_pv(t, slot_of(iv), j == lo[t]);
-              if (t == 1) tc_commit(bar_empty(slot_of(iv)));
+              if (t == 1) tc_commit_w(bar_empty(slot_of(iv)));
               if (more && in_range(t, j + 1)) issue_s(t, slot_of(ik));
-              if (more && t == 1) tc_commit(bar_empty(slot_of(ik)));
+              if (more && t == 1) tc_commit_w(bar_empty(slot_of(ik)));
             }
           }
         }

@@ -228,8 +228,8 @@ int fa_abi_struct_size(int32_t which);
 
 /* Message for the last non-zero status returned on this thread. */
 const char* fa_last_error(void);
-/* Names of the kernels that the last fa_fwd / fa_bwd / fa_fwd_kvcache[_noalloc] call of this thread
-   launched, e.g. "fwd_tc", "fwd_generic+combine", "bwd_tc+bwd_dq_tc", "bwd_wide_tc", "decode+combine"
+/* Names of the kernels that the last fa_fwd / fa_bwd / fa_fwd_kvcache[_noalloc] call of this process
+   (whichever thread made it) launched, e.g. "fwd_tc", "fwd_generic+combine", "bwd_tc+bwd_dq_tc", "bwd_wide_tc", "decode+combine"
    (no counterpart in the reference; tests use it to pin a case to the kernel it is meant to cover). */
 const char* fa_last_path(void);
 /* Compile-time facts: "sm_100a", kernel list, build flags. */

@@ -39,3 +39,22 @@ def make_qkv(B, Sq, Sk, H, Hk, D, dtype, seed=0, device="cuda"):
     v = torch.randn(B, Sk, Hk, D, generator=g).to(dtype).to(device)
     do = torch.randn(B, Sq, H, D, generator=g).to(dtype).to(device)
     return q, k, v, do
+
+
+def kvcache_truth(q, k_cache, v_cache, k_new, v_new, cos, sin, cache_seqlens, rotary_interleaved=False, causal=True):
+    """(out fp32 truth, out 16-bit yardstick, expected K cache, expected V cache) of a decode step with append +
+    rotary.  The kernel rotates in fp32 and rounds once, as the reference's rotary op does in its own KV-cache test
+    (tests/test_flash_attn.py:1758-1797): the rotation is therefore done here in fp32 and rounded to the storage
+    type before the attention oracle runs."""
+    B, Sq, H, D = q.shape
+    dt = q.dtype
+    cosf, sinf = cos.float(), sin.float()
+    if causal:
+        q_r = O.rotary_oracle(q.float(), cosf, sinf, cache_seqlens, rotary_interleaved).to(dt)
+    else:
+        q_r = O.rotary_oracle(q.float().reshape(B, 1, Sq * H, D), cosf, sinf, cache_seqlens, rotary_interleaved).reshape(B, Sq, H, D).to(dt)
+    k_r = O.rotary_oracle(k_new.float(), cosf, sinf, cache_seqlens, rotary_interleaved).to(dt)
+    kw = dict(cache_seqlens=cache_seqlens, causal=causal)
+    out_t, kc_t, vc_t = O.kvcache_oracle(q_r, k_cache, v_cache, k_r, v_new, None, None, **kw)
+    out_l, _, _ = O.kvcache_oracle(q_r, k_cache, v_cache, k_r, v_new, None, None, upcast=False, reorder_ops=True, **kw)
+    return out_t, out_l, kc_t, vc_t

@@ -11,7 +11,7 @@ import math
 import pytest
 import torch
 
-from gpu_util import assert_within
+from gpu_util import assert_within, kvcache_truth
 from oracle import attention_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -150,10 +150,7 @@ def test_decode_step_batch64_capacity32768():
     for b in picks:
         kb, vb = before[b]
         sl = slice(b, b + 1)
-        args = (q[sl], kb[None], vb[None], kn[sl], vn[sl], cos, sin)
-        o_t, kc_t, vc_t = O.kvcache_oracle(*args, cache_seqlens=lens[sl], causal=True, rotary_interleaved=False)
-        o_l, _, _ = O.kvcache_oracle(*args, cache_seqlens=lens[sl], causal=True, rotary_interleaved=False, upcast=False,
-                                     reorder_ops=True)
+        o_t, o_l, kc_t, vc_t = kvcache_truth(q[sl], kb[None], vb[None], kn[sl], vn[sl], cos, sin, lens[sl])
         assert_within(out[sl], o_t, o_l, mult=3, what="out seq %d (len %d)" % (b, int(lens[b])))
         assert torch.equal(vc[sl], vc_t), "V cache line %d" % b
         assert torch.allclose(kc[sl].float(), kc_t.float(), atol=1e-3, rtol=1e-3), "K cache line %d" % b

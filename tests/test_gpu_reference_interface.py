@@ -12,7 +12,7 @@ import os
 import pytest
 import torch
 
-from gpu_util import assert_within, oracle_fwd_bwd
+from gpu_util import assert_within, kvcache_truth, oracle_fwd_bwd
 from oracle import attention_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -148,9 +148,7 @@ def test_flash_attn_with_kvcache(ref):
     kc0, vc0 = kc.clone(), vc.clone()
     out = ref.flash_attn_with_kvcache(q, kc, vc, kn, vn, rotary_cos=cos, rotary_sin=sin, cache_seqlens=lens, causal=True,
                                       rotary_interleaved=False)
-    o_t, kc_t, vc_t = O.kvcache_oracle(q, kc0, vc0, kn, vn, cos, sin, cache_seqlens=lens, causal=True, rotary_interleaved=False)
-    o_l, _, _ = O.kvcache_oracle(q, kc0, vc0, kn, vn, cos, sin, cache_seqlens=lens, causal=True, rotary_interleaved=False,
-                                 upcast=False, reorder_ops=True)
+    o_t, o_l, kc_t, vc_t = kvcache_truth(q, kc0, vc0, kn, vn, cos, sin, lens)
     assert_within(out, o_t, o_l, mult=3, what="kvcache out")
     assert torch.equal(vc, vc_t)
     assert torch.allclose(kc.float(), kc_t.float(), atol=1e-3, rtol=1e-3)
