@@ -164,13 +164,13 @@ int fa_abi_struct_size(int32_t which) {
 
 int fa_fwd_num_splits(int32_t batch, int32_t heads, int32_t seqlen_q, int32_t seqlen_k, int32_t head_dim,
                       int32_t num_sms) {
-  // Same search as num_splits_heuristic (flash_api.cpp:206-246) on this library's tile sizes
-  // (64 query rows, 64 keys per block of the split kernel): with enough CTAs to fill 80 % of the
-  // SMs do not split; otherwise take the smallest split count within 85 % of the best wave
-  // efficiency.
-  (void)head_dim;
+  // Same search as num_splits_heuristic (flash_api.cpp:206-246) on this library's tile sizes (a work
+  // item of the tensor-core kernel is 256 query rows, 128 above head dim 128, and walks 128-key
+  // blocks): with enough items to fill 80 % of the SMs do not split; otherwise take the smallest
+  // split count within 85 % of the best wave efficiency.
   if (num_sms <= 0) num_sms = fa_host::sm_count();
-  const int m_blocks = (seqlen_q + 63) / 64, n_blocks = (seqlen_k + 63) / 64;
+  const int rows = head_dim > 128 ? 128 : 256;
+  const int m_blocks = (seqlen_q + rows - 1) / rows, n_blocks = (seqlen_k + 127) / 128;
   const int ctas = batch * heads * m_blocks;
   if (ctas >= 0.8f * num_sms) return 1;
   int max_splits = 128;
@@ -222,12 +222,14 @@ int fa_fwd(const FaFwdArgs* a, fa_stream_t stream) {
   }
   if (a->seqlen_q == 0 || a->batch == 0) return 0;
   if (refuse_if_device_failed()) return 3;
-  if (a->num_splits <= 1 && !fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::fwd_tc_eligible(*a)) {
-    g_last_path = "fwd_tc";
-    return fa::fwd_tc(*a, st);
+  int rc;
+  if (!fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::fwd_tc_eligible(*a)) {
+    g_last_path = a->num_splits > 1 ? "fwd_tc+combine" : "fwd_tc";
+    rc = fa::fwd_tc(*a, st);
+  } else {
+    g_last_path = a->num_splits > 1 ? "fwd_generic+combine" : "fwd_generic";
+    rc = fa::fwd_generic(*a, st);
   }
-  g_last_path = a->num_splits > 1 ? "fwd_generic+combine" : "fwd_generic";
-  int rc = fa::fwd_generic(*a, st);
   if (rc) return rc;
   if (a->num_splits > 1)
     return fa::combine(a->out_accum, a->lse_accum, a->out, a->softmax_lse, a->lse_seqlen, a->num_splits, a->batch,

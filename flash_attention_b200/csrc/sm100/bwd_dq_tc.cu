@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
       // Each MMA group is issued as soon as its inputs exist and its output columns are free:
       //   S(j+1) once the compute warps hold S(j) in registers, dP(j+1) once they hold dP(j),
       //   dQ(j) once dS(j) is in its buffer.
-      if (lane == 0 && run) {
+      if (run) {  // the whole warp runs the loops (see mma_ss_w); one elected lane issues
         constexpr int F = QFmt<T>::kIdesc;
         constexpr uint32_t idesc_s = make_idesc(kB, kB, F, 0, 0);   // S, dP: K-major x K-major, N = 128 keys
         constexpr uint32_t idesc_dq = make_idesc(kB, DH, F, 0, 1);  // dQ: A in TMEM, B MN-major, N = DH
@@ -302,41 +302,41 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_tc_kernel(const __grid_con
         auto moff = [](int kk) { return (uint32_t)((kk * 2048) >> 4) + kMn; };                          // MN-major k-step
         auto issue_s = [&](uint32_t d_col, uint32_t a_lo, uint32_t b_lo, uint32_t bar) {
 #pragma unroll
-          for (int kk = 0; kk < DH / 16; ++kk) mma_ss(tmem + d_col, dsc(a_lo + koff(kk)), dsc(b_lo + koff(kk)), idesc_s, kk > 0);
-          tc_commit(bar);
+          for (int kk = 0; kk < DH / 16; ++kk) mma_ss_w(tmem + d_col, dsc(a_lo + koff(kk)), dsc(b_lo + koff(kk)), idesc_s, kk > 0);
+          tc_commit_w(bar);
         };
-        bool ok = mbar_wait(bar_qdo, 0, W_Q_QDO, abort_flag);
+        bool ok = mbar_wait_w(bar_qdo, 0, W_Q_QDO, abort_flag);
         if (warp == kWarpMma) {
           // ---- S and dP: block j+1 as soon as the compute warps hold block j's in registers
           for (int j = 0; j < iters && ok; ++j) {
             const int ks = j % NSK, vs = j % NSV;
-            if (j > 0) ok = mbar_wait(bar_sread, (j - 1) & 1, W_Q_S, abort_flag);
-            if (ok) ok = mbar_wait(bar_k_full(ks), (j / NSK) & 1, W_Q_KV_FULL, abort_flag);
+            if (j > 0) ok = mbar_wait_w(bar_sread, (j - 1) & 1, W_Q_S, abort_flag);
+            if (ok) ok = mbar_wait_w(bar_k_full(ks), (j / NSK) & 1, W_Q_KV_FULL, abort_flag);
             if (!ok) break;
             tc_fence_after();
             issue_s(C::COL_S, oQ, oK + ks * kTile16, bar_s);
-            if (j > 0) ok = mbar_wait(bar_dpread, (j - 1) & 1, W_Q_DP, abort_flag);
-            if (ok) ok = mbar_wait(bar_v_full(vs), (j / NSV) & 1, W_Q_KV_FULL, abort_flag);
+            if (j > 0) ok = mbar_wait_w(bar_dpread, (j - 1) & 1, W_Q_DP, abort_flag);
+            if (ok) ok = mbar_wait_w(bar_v_full(vs), (j / NSV) & 1, W_Q_KV_FULL, abort_flag);
             if (!ok) break;
             tc_fence_after();
             issue_s(C::COL_DP, oDO, oV + vs * kTile16, bar_dp);
-            tc_commit(bar_v_empty(vs));
+            tc_commit_w(bar_v_empty(vs));
           }
         } else {
           // ---- dQ += dS K: the two warpgroups' halves of dS are the two 32-column halves of the block's buffer.
           // Its commit releases the K tile, which S(j) of the other issuer read as well: dS(j) was computed from S(j).
           for (int j = 0; j < iters && ok; ++j) {
             const int ks = j % NSK;
-            ok = mbar_wait(bar_ds, j & 1, W_Q_DS, abort_flag);
+            ok = mbar_wait_w(bar_ds, j & 1, W_Q_DS, abort_flag);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < kB / 16; ++kk)
-              mma_ts(tmem + C::COL_DQ, tmem + C::COL_DS + (j & 1) * 64 + kk * 8, dsc(oK + ks * kTile16 + moff(kk)), idesc_dq,
+              mma_ts_w(tmem + C::COL_DQ, tmem + C::COL_DS + (j & 1) * 64 + kk * 8, dsc(oK + ks * kTile16 + moff(kk)), idesc_dq,
                      (j > 0) || kk > 0);
-            tc_commit(bar_k_empty(ks));
+            tc_commit_w(bar_k_empty(ks));
           }
-          if (ok) tc_commit(bar_done);
+          if (ok) tc_commit_w(bar_done);
         }
       }
     }

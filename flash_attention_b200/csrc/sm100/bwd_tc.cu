@@ -393,7 +393,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
       // issues the chain dV(i) | dK(i) | dP^T(i+1): dV(i) waits for P^T(i), dK(i) for dS^T(i); both sit over dP^T(i),
       // and the MMAs of one thread execute in order, so dP^T(i+1) overwrites them only after they were read.
       // MMAs of the two threads are not ordered among themselves and need not be.
-      if (lane == 0 && run) {
+      if (run) {  // the whole warp runs the loops (see mma_ss_w); one elected lane issues
         constexpr int F = BFmt<T>::kIdesc;
         constexpr uint32_t idesc_st = make_idesc(kB, kB, F, 0, 0);   // S^T, dP^T: K-major x K-major, N = 128 queries
         constexpr uint32_t idesc_dv = make_idesc(kB, DH, F, 0, 1);   // dV, dK: A K-major (or TMEM), B MN-major, N = DH
@@ -409,21 +409,21 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
         auto moff = [](int kk) { return (uint32_t)((kk * 2048) >> 4) + kMn; };                          // MN-major k-step
         auto issue_st = [&](uint32_t d_col, uint32_t a_lo, uint32_t b_lo, uint32_t bar) {
 #pragma unroll
-          for (int kk = 0; kk < DH / 16; ++kk) mma_ss(tmem + d_col, dsc(a_lo + koff(kk)), dsc(b_lo + koff(kk)), idesc_st, kk > 0);
-          tc_commit(bar);
+          for (int kk = 0; kk < DH / 16; ++kk) mma_ss_w(tmem + d_col, dsc(a_lo + koff(kk)), dsc(b_lo + koff(kk)), idesc_st, kk > 0);
+          tc_commit_w(bar);
         };
-        bool ok = mbar_wait(bar_kv, 0, W_B_KV, abort_flag);
+        bool ok = mbar_wait_w(bar_kv, 0, W_B_KV, abort_flag);
         if (warp == kWarpMmaS) {
           for (int it = 0; it < iters && ok; ++it) {
             const int qs = it % NSQ;
-            if (it > 0) ok = mbar_wait(bar_sread, (it - 1) & 1, W_B_S, abort_flag);
-            if (ok) ok = mbar_wait(bar_q_full(qs), (it / NSQ) & 1, W_B_QDO_FULL, abort_flag);
+            if (it > 0) ok = mbar_wait_w(bar_sread, (it - 1) & 1, W_B_S, abort_flag);
+            if (ok) ok = mbar_wait_w(bar_q_full(qs), (it / NSQ) & 1, W_B_QDO_FULL, abort_flag);
             if (!ok) break;
             tc_fence_after();
             issue_st(C::COL_S, oK, oQ + qs * kTile16, bar_s);
           }
         } else {
-          if (ok) ok = mbar_wait(bar_do_full(0), 0, W_B_QDO_FULL, abort_flag);
+          if (ok) ok = mbar_wait_w(bar_do_full(0), 0, W_B_QDO_FULL, abort_flag);
           if (ok) {
             tc_fence_after();
             issue_st(C::COL_DP, oV, oDO, bar_dp);
@@ -433,26 +433,26 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_tc_kernel(const __grid_consta
             const int qs = it % NSQ, os = it % NSO, nos = (it + 1) % NSO;
             // P^T(it) is in TMEM over dP^T(it): dV += P^T dO (the warpgroups' halves sit at columns 0 and 64 of
             // the dP^T range); that was the last use of this dO tile
-            ok = mbar_wait(bar_p, it & 1, W_B_PDS, abort_flag);
+            ok = mbar_wait_w(bar_p, it & 1, W_B_PDS, abort_flag);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < kB / 16; ++kk)
-              mma_ts(tmem + C::COL_DV, tmem + C::COL_DP + (kk >> 2) * 64 + (kk & 3) * 8, dsc(oDO + os * kTile16 + moff(kk)),
+              mma_ts_w(tmem + C::COL_DV, tmem + C::COL_DP + (kk >> 2) * 64 + (kk & 3) * 8, dsc(oDO + os * kTile16 + moff(kk)),
                      idesc_dv, (it > 0) || kk > 0);
-            tc_commit(bar_do_empty(os));
+            tc_commit_w(bar_do_empty(os));
             // dS^T(it) is in TMEM next to P^T(it) (columns 32 and 96 of the dP^T range): dK += dS^T Q, the last
             // use of this Q tile (S^T(it) of the other issuer read it too: P^T(it) was computed from it)
-            ok = mbar_wait(bar_ds, it & 1, W_B_PDS, abort_flag);
+            ok = mbar_wait_w(bar_ds, it & 1, W_B_PDS, abort_flag);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < kB / 16; ++kk)
-              mma_ts(tmem + C::COL_DK, tmem + C::COL_DP + 32 + (kk >> 2) * 64 + (kk & 3) * 8, dsc(oQ + qs * kTile16 + moff(kk)),
+              mma_ts_w(tmem + C::COL_DK, tmem + C::COL_DP + 32 + (kk >> 2) * 64 + (kk & 3) * 8, dsc(oQ + qs * kTile16 + moff(kk)),
                      idesc_dv, (it > 0) || kk > 0);
-            tc_commit(bar_q_empty(qs));
+            tc_commit_w(bar_q_empty(qs));
             if (more) {
-              ok = mbar_wait(bar_do_full(nos), ((it + 1) / NSO) & 1, W_B_QDO_FULL, abort_flag);
+              ok = mbar_wait_w(bar_do_full(nos), ((it + 1) / NSO) & 1, W_B_QDO_FULL, abort_flag);
               if (!ok) break;
               tc_fence_after();
               issue_st(C::COL_DP, oV, oDO + nos * kTile16, bar_dp);

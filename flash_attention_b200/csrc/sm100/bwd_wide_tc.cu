@@ -433,7 +433,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_wide_tc_kernel(const __grid_c
       //   X2(j+1): once they hold X2(j) and its tile has landed
       //   last product of block j: once W(j) is in its buffer; its commit releases the tile X1(j) read as well
       //   (X1(j) is complete by then: W(j) was computed from it)
-      if (lane == 0 && run) {
+      if (run) {  // the whole warp runs the loops (see mma_ss_w); one elected lane issues
         constexpr int F = WFmt<T>::kIdesc;
         constexpr uint32_t idesc_x = make_idesc(kR, kN, F, 0, 0);    // X1, X2: K-major x K-major, N = 64 streamed rows
         constexpr uint32_t idesc_o = make_idesc(kR, kDH, F, 0, 1);   // last product: A in TMEM, B MN-major, N = 256
@@ -451,62 +451,62 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_wide_tc_kernel(const __grid_c
         auto issue_x = [&](uint32_t d_col, uint32_t a_lo, uint32_t b_lo) {
 #pragma unroll
           for (int kk = 0; kk < kDH / 16; ++kk)
-            mma_ss(tmem + d_col, dsc(a_lo + koff_a(kk)), dsc(b_lo + koff_b(kk)), idesc_x, kk > 0);
+            mma_ss_w(tmem + d_col, dsc(a_lo + koff_a(kk)), dsc(b_lo + koff_b(kk)), idesc_x, kk > 0);
         };
         auto issue_out = [&](int j, uint32_t b_lo) {
           // the two warpgroups' halves of W are the two 16-column halves of this block's buffer
 #pragma unroll
           for (int kk = 0; kk < kN / 16; ++kk)
-            mma_ts(tmem + C::COL_OUT, tmem + C::COL_W + (j & 1) * 32 + kk * 8, dsc(b_lo + moff(kk)), idesc_o, (j > 0) || kk > 0);
+            mma_ts_w(tmem + C::COL_OUT, tmem + C::COL_W + (j & 1) * 32 + kk * 8, dsc(b_lo + moff(kk)), idesc_o, (j > 0) || kk > 0);
         };
-        bool ok = mbar_wait(bar_a, 0, W_W_A, abort_flag);
+        bool ok = mbar_wait_w(bar_a, 0, W_W_A, abort_flag);
         if (warp == kWarpMmaX1) {
           // ---- X1 products
           for (int j = 0; j < iters && ok; ++j) {
             const int s1 = j % NS1;
-            if (j > 0) ok = mbar_wait(bar_x1read, (j - 1) & 1, W_W_READ, abort_flag);
-            if (ok) ok = mbar_wait(bar_b1_full(s1), (j / NS1) & 1, W_W_B_FULL, abort_flag);
+            if (j > 0) ok = mbar_wait_w(bar_x1read, (j - 1) & 1, W_W_READ, abort_flag);
+            if (ok) ok = mbar_wait_w(bar_b1_full(s1), (j / NS1) & 1, W_W_B_FULL, abort_flag);
             if (!ok) break;
             tc_fence_after();
             issue_x(C::COL_X1, oA1, oB1 + s1 * kTileB16);
-            tc_commit(bar_x1);
-            if (PASS == PASS_DV) tc_commit(bar_b1_empty(s1));
+            tc_commit_w(bar_x1);
+            if (PASS == PASS_DV) tc_commit_w(bar_b1_empty(s1));
           }
         } else {
           // ---- X2 products and the last product of every block
           if (PASS != PASS_DV) {
-            if (ok) ok = mbar_wait(bar_b2_full(0), 0, W_W_B_FULL, abort_flag);
+            if (ok) ok = mbar_wait_w(bar_b2_full(0), 0, W_W_B_FULL, abort_flag);
             if (ok) {
               tc_fence_after();
               issue_x(C::COL_X2, oA2, oB2);
-              tc_commit(bar_x2);
-              tc_commit(bar_b2_empty(0));
+              tc_commit_w(bar_x2);
+              tc_commit_w(bar_b2_empty(0));
             }
           }
           for (int j = 0; j < iters && ok; ++j) {
             if (PASS != PASS_DV && j + 1 < iters) {
               const int n2 = (j + 1) % NS2;
-              ok = mbar_wait(bar_x2read, j & 1, W_W_READ, abort_flag);
-              if (ok) ok = mbar_wait(bar_b2_full(n2), ((j + 1) / NS2) & 1, W_W_B_FULL, abort_flag);
+              ok = mbar_wait_w(bar_x2read, j & 1, W_W_READ, abort_flag);
+              if (ok) ok = mbar_wait_w(bar_b2_full(n2), ((j + 1) / NS2) & 1, W_W_B_FULL, abort_flag);
               if (!ok) break;
               tc_fence_after();
               issue_x(C::COL_X2, oA2, oB2 + n2 * kTileB16);
-              tc_commit(bar_x2);
-              tc_commit(bar_b2_empty(n2));
+              tc_commit_w(bar_x2);
+              tc_commit_w(bar_b2_empty(n2));
             }
-            ok = mbar_wait(bar_w, j & 1, W_W_W, abort_flag);
-            if (ok && PASS == PASS_DV) ok = mbar_wait(bar_b2_full(j % NS2), (j / NS2) & 1, W_W_B_FULL, abort_flag);
+            ok = mbar_wait_w(bar_w, j & 1, W_W_W, abort_flag);
+            if (ok && PASS == PASS_DV) ok = mbar_wait_w(bar_b2_full(j % NS2), (j / NS2) & 1, W_W_B_FULL, abort_flag);
             if (!ok) break;
             tc_fence_after();
             if (PASS == PASS_DV) {
               issue_out(j, oB2 + (j % NS2) * kTileB16);
-              tc_commit(bar_b2_empty(j % NS2));
+              tc_commit_w(bar_b2_empty(j % NS2));
             } else {
               issue_out(j, oB1 + (j % NS1) * kTileB16);
-              tc_commit(bar_b1_empty(j % NS1));
+              tc_commit_w(bar_b1_empty(j % NS1));
             }
           }
-          if (ok) tc_commit(bar_done);
+          if (ok) tc_commit_w(bar_done);
         }
       }
     }

@@ -113,6 +113,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
       if (mbar_try_wait_parked(bar, parity, 2000)) return true;
     } else if (mode == 2) {
       __nanosleep(40);
+    } else if (mode == 3) {
+      // a warp that waits for long stretches (an epilogue or bookkeeping role) must not compete for issue
+      // slots with the warps that do the arithmetic on the same scheduler
+      __nanosleep(400);
     }
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 63u) == 0) {
@@ -123,6 +127,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
       }
     }
   }
+}
+
+// For a warp that must stay converged (an MMA-issuing warp): every lane waits, and all lanes get the
+// same answer even if a wait gave up for some lanes just as the phase completed for others.
+__device__ __forceinline__ bool mbar_wait_w(uint32_t bar, uint32_t parity, int code, volatile int* abort_flag) {
+  const bool ok = mbar_wait(bar, parity, code, abort_flag);
+  return __all_sync(0xffffffffu, ok);
 }
 
 __device__ __forceinline__ bool mbar_wait_probed(uint32_t hit, uint32_t bar, uint32_t parity, int code,
@@ -246,6 +257,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
