@@ -41,7 +41,6 @@ class FaFwdArgs(C.Structure):
         ("num_splits", c_i32),
         ("lse_accum", c_vp), ("out_accum", c_vp),
         ("use_mask_shift", c_i32), ("mask_shift", c_i32),
-        ("tile_counter", c_vp),
     ]
 
 

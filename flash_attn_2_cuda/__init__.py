@@ -161,8 +161,6 @@ def fwd(q, k, v, out_, p_dropout, softmax_scale, is_causal, window_size_left, wi
             if p is not None:
                 a.s_dmask, a.sdmask_rows, a.sdmask_cols = ptr(p), p.shape[2], p.shape[3]
             a.num_splits = 1
-            counter = torch.zeros(2, dtype=torch.int32, device=q.device)  # work counter of the persistent kernel
-            a.tile_counter = ptr(counter)
             keep = None
             if p_dropout == 0.0:  # flash_api.cpp:373-389
                 ns = lib().fa_fwd_num_splits(batch, heads, seqlen_q, seqlen_k, d, _sm_count(q.device))
@@ -174,7 +172,7 @@ def fwd(q, k, v, out_, p_dropout, softmax_scale, is_causal, window_size_left, wi
                     a.num_splits, a.lse_accum, a.out_accum = ns, ptr(lse_acc), ptr(out_acc)
                     keep = (lse_acc, out_acc)
             check(lib().fa_fwd(ctypes.byref(a), _stream(q)), "flash_attn_2_cuda.fwd")
-            del keep, counter
+            del keep
         else:
             # no keys: flash_api.cpp:409-414
             out.zero_()
@@ -261,11 +259,8 @@ def varlen_fwd(q, k, v, out_, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seql
         if p is not None:
             a.s_dmask, a.sdmask_rows, a.sdmask_cols = ptr(p), p.shape[2], p.shape[3]
         a.num_splits = 1
-        counter = torch.zeros(2, dtype=torch.int32, device=q.device)  # work counter of the persistent kernel
-        a.tile_counter = ptr(counter)
         if max_seqlen_q > 0:
             check(lib().fa_fwd(ctypes.byref(a), _stream(q)), "flash_attn_2_cuda.varlen_fwd")
-        del counter
 
     out_padded = out
     if d_og % 8 != 0:

@@ -81,13 +81,6 @@ typedef struct FaFwdArgs {
      the reference has no ring attention). */
   int32_t use_mask_shift;
   int32_t mask_shift;
-  /* Optional work counter of the persistent tensor-core kernel: two int32 in device memory, zero on
-     entry, used by no other launch while this one runs.  With it the CTAs draw their work items
-     dynamically (balanced for causal masks and packed sequences of unequal length); NULL selects a
-     fixed round-robin assignment.  The kernel sets both words back to zero before it ends, so a
-     caller may hand the same two words to its next call on the same stream.  (The reference's
-     kernels are not persistent and have no counterpart.) */
-  int32_t* tile_counter;
 } FaFwdArgs;
 
 /* Backward.  Replaces mha_bwd (flash_api.cpp:609-811) and mha_varlen_bwd (flash_api.cpp:813-1036),
