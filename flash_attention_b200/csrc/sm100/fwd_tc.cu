@@ -7,8 +7,7 @@
 // Warp roles (384 threads):
 //   warps 0-3   softmax of tile 0  (one thread per query row; tcgen05.ld 32x32b gives a thread its row)
 //   warps 4-7   softmax of tile 1
-//   warp  8     TMA producer: Q tiles once, then K(j), V(j), K(j+1), ... through a ring of slots; it starts
-//               as soon as the barriers exist, while warp 10 is still allocating tensor memory
+//   warp  8     TMA producer: Q tiles once, then K(j), V(j), K(j+1), ... through a ring of slots
 //   warp  9     MMA issuer: the warp stays converged, one elected lane issues every tcgen05.mma
 //   warp  10    owns the TMEM allocation
 // TMEM columns (fp32): S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).  P (16-bit) is
@@ -59,7 +58,7 @@ constexpr int kBN = 128;  // keys per K/V tile
 constexpr int kChunkBytes = 128 * 128;  // [128 rows][64 x 16-bit]: one swizzled TMA box
 constexpr float kRescaleThreshold = 8.f;
 
-enum WaitCode { W_QFULL = 11, W_KVFULL = 12, W_KVEMPTY = 13, W_SFULL = 14, W_PFULL = 15, W_OFULL = 16, W_TMEM = 17 };
+enum WaitCode { W_QFULL = 11, W_KVFULL = 12, W_KVEMPTY = 13, W_SFULL = 14, W_PFULL = 15, W_OFULL = 16 };
 
 template <int DH>
 struct Cfg {
@@ -70,7 +69,7 @@ struct Cfg {
   static constexpr int NT = DH > 128 ? 1 : 2;
   static constexpr int STAGES = DH > 128 ? 2 : (DH == 128 ? 4 : 8);
   static constexpr int SMEM_TILES = (NT + STAGES) * TILE_BYTES;
-  static constexpr int NBAR = 2 + 2 * STAGES + 8 + 1;
+  static constexpr int NBAR = 2 + 2 * STAGES + 8;
   static constexpr int SMEM_BYTES = SMEM_TILES + NBAR * 8 + 32 + 1024;  // + barriers, tmem ptr / abort block, align slack
   static constexpr int TMEM_COLS = 512;
   static constexpr int COL_S0 = 0, COL_S1 = 128, COL_O0 = 256, COL_O1 = 256 + DH;
@@ -111,7 +110,6 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
   auto bar_pfull = [&](int t) { return bar0 + 8 * (2 + 2 * C::STAGES + 2 + t); };
   auto bar_ofull = [&](int t) { return bar0 + 8 * (2 + 2 * C::STAGES + 4 + t); };
   auto bar_pfull_b = [&](int t) { return bar0 + 8 * (2 + 2 * C::STAGES + 6 + t); };
-  const uint32_t bar_tmem = bar0 + 8 * (2 + 2 * C::STAGES + 8);  // the TMEM address has been published
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + C::SMEM_TILES + C::NBAR * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::SMEM_TILES + C::NBAR * 8 + 4);
 
@@ -171,7 +169,6 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
       mbar_init(bar_pfull_b(t), 4);
       mbar_init(bar_ofull(t), 1);
     }
-    mbar_init(bar_tmem, 1);
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(bar_full(s), 1);
       mbar_init(bar_empty(s), 1);
@@ -179,22 +176,14 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
     fence_barrier_init();
     fence_proxy_async();
   }
-  __syncthreads();  // the barriers exist
-  // Allocating tensor memory can take thousands of cycles (it waits for the CTA before on this SM to give its
-  // columns back).  The TMA producer does not need it and starts loading at once; everyone else waits here.
-  uint32_t tmem = 0;
   if (warp == 10) {
     tmem_alloc(smem_addr(const_cast<uint32_t*>(tmem_ptr_smem)), C::TMEM_COLS);
     tmem_relinquish();
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_tmem);
   }
-  if (warp != 8) {
-    mbar_wait(bar_tmem, 0, W_TMEM, abort_flag);  // on failure the abort flag is set and every later wait fails fast
-    tc_fence_after();
-    tmem = *tmem_ptr_smem;
-  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_ptr_smem;
 
   const float scale_log2 = a.softmax_scale * kLog2e;
 
@@ -362,16 +351,24 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
         }
         unsigned char* stage = smem + t * C::TILE_BYTES;  // the Q tile of this warpgroup is no longer read
         constexpr int ROWB = DH * 2;
+        // O leaves tensor memory 128 columns per round trip (a trip costs ~250 cycles whatever its size)
+        constexpr int OB = DH < 128 ? DH : 128;
+        uint32_t ob[OB / 32][32];
 #pragma unroll
         for (int c0 = 0; c0 < DH; c0 += 32) {
-          uint32_t o[32];
-          if (have_o) {
-            tmem_ld32(tO + c0, o);
-            tmem_wait_ld();
-          } else {
+          if (c0 % OB == 0) {
+            if (have_o) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = 0u;
+              for (int c = 0; c < OB; c += 32) tmem_ld32(tO + c0 + c, ob[c / 32]);
+              tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int c = 0; c < OB / 32; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) ob[c][i] = 0u;
+            }
           }
+          const uint32_t(&o)[32] = ob[(c0 % OB) / 32];
           if (P.num_splits > 1) {  // normalised fp32 partial, straight from the registers (rows are contiguous)
             if (row < si.sq) {
               float* oa = a.out_accum +
@@ -482,18 +479,8 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
         auto in_range = [&](int t, int j) { return j >= lo[t] && j < hi[t]; };
         auto slot_of = [&](int idx) { return idx % C::STAGES; };
         auto par_of = [&](int idx) { return (uint32_t)((idx / C::STAGES) & 1); };
-        // A wait costs this warp 150+ cycles even when the barrier has long completed (a round trip to shared
-        // memory between instructions that compete for issue slots with the softmax warps).  So each barrier is
-        // tested one MMA group ahead of its use: the answer travels while the group before is being issued (the
-        // issue blocks at the pace of the tensor pipe), and only a miss falls back to a real wait.  A hit stays
-        // valid until this warp consumes the phase: no producer can run more than one phase ahead of it.
-        auto waitp = [&](uint32_t& hit, uint32_t bar, uint32_t par, int code) -> bool {
-          const uint32_t h = hit;
-          hit = 0;
-          if (h) return true;
-          return mbar_wait_w(bar, par, code, abort_flag);
-        };
-        uint32_t h_v = 0, h_k = 0, h_pa[2] = {0, 0}, h_pb[2] = {0, 0};
+        // (Testing each barrier one MMA group ahead of its use, so that the answer travels while the group before
+        // is being issued, was measured here and lost 3-5 %: the tests themselves take issue slots of this warp.)
         if (nblk > 0) {
           for (int t = 0; t < C::NT && ok; ++t)
             if (hi[t] > lo[t]) ok = mbar_wait_w(bar_qfull(t), 0, W_QFULL, abort_flag);
@@ -509,35 +496,25 @@ __global__ void __launch_bounds__(384, 1) fwd_tc_kernel(const __grid_constant__ 
             const int iv = 2 * (j - J_lo) + 1;  // ring index of V(j)
             const int ik = iv + 1;              // ring index of K(j+1)
             const bool more = j + 1 < J_hi;
-            ok = waitp(h_v, bar_full(slot_of(iv)), par_of(iv), W_KVFULL);
-            if (ok && more) ok = waitp(h_k, bar_full(slot_of(ik)), par_of(ik), W_KVFULL);
-            h_k = 0;
+            ok = mbar_wait_w(bar_full(slot_of(iv)), par_of(iv), W_KVFULL, abort_flag);
+            if (ok && more) ok = mbar_wait_w(bar_full(slot_of(ik)), par_of(ik), W_KVFULL, abort_flag);
             if (!ok) break;
 #pragma unroll
             for (int t = 0; t < C::NT; ++t) {
               if (!ok) break;
               if (in_range(t, j)) {
                 const uint32_t par = (uint32_t)(p_iter[t] & 1);
-                ok = waitp(h_pa[t], bar_pfull(t), par, W_PFULL);
+                ok = mbar_wait_w(bar_pfull(t), par, W_PFULL, abort_flag);
                 if (!ok) break;
-                if (!h_pb[t]) h_pb[t] = mbar_test(bar_pfull_b(t), par);
                 tc_fence_after();
                 issue_pv_half(t, slot_of(iv), j == lo[t], 0);
-                ok = waitp(h_pb[t], bar_pfull_b(t), par, W_PFULL);
+                ok = mbar_wait_w(bar_pfull_b(t), par, W_PFULL, abort_flag);
                 if (!ok) break;
-                if (C::NT == 2 && t == 0 && in_range(1, j)) h_pa[1] = mbar_test(bar_pfull(1), (uint32_t)(p_iter[1] & 1));
                 tc_fence_after();
                 issue_pv_half(t, slot_of(iv), j == lo[t], 1);
                 ++p_iter[t];
               }
               if (t == C::NT - 1) tc_commit_w(bar_empty(slot_of(iv)));
-              // tests whose answers travel while the (long) S group below is being issued
-              if (C::NT == 2 && t == 0 && in_range(1, j)) h_pb[1] = mbar_test(bar_pfull_b(1), (uint32_t)(p_iter[1] & 1));
-              if (t == C::NT - 1 && more) {
-                h_v = mbar_test(bar_full(slot_of(iv + 2)), par_of(iv + 2));
-                if (j + 2 < J_hi) h_k = mbar_test(bar_full(slot_of(ik + 2)), par_of(ik + 2));
-                if (in_range(0, j + 1)) h_pa[0] = mbar_test(bar_pfull(0), (uint32_t)(p_iter[0] & 1));
-              }
               if (more && in_range(t, j + 1)) issue_s(t, slot_of(ik));
               if (more && t == C::NT - 1) tc_commit_w(bar_empty(slot_of(ik)));
             }
