@@ -65,6 +65,7 @@ class FaBwdArgs(C.Structure):
         ("use_mask_shift", c_i32), ("mask_shift", c_i32),
         ("accumulate_dkv", c_i32),
         ("dk_accum", c_vp), ("dv_accum", c_vp),
+        ("parts", c_i32),
     ]
 
 

@@ -34,7 +34,7 @@ int decode_noalloc_fit(const FaKvcacheArgs& a, int num_splits);
 int decode_run_noalloc(const FaKvcacheArgs& a, int num_splits, cudaStream_t st);
 size_t decode_noalloc_capacity();
 int bwd_dq_tc_main(const FaBwdArgs& a, cudaStream_t st);
-int bwd_wide_tc_main(const FaBwdArgs& a, cudaStream_t st);
+int bwd_wide_tc_main(const FaBwdArgs& a, int parts, cudaStream_t st);
 // device status word (sm100/status.cu)
 int status_peek();
 int status_read(bool clear);
@@ -257,15 +257,18 @@ int fa_bwd(const FaBwdArgs* a, fa_stream_t stream) {
   if (a->seqlen_q == 0 || a->batch == 0) return 0;
   if (refuse_if_device_failed()) return 3;
   const bool tc = a->seqlen_k > 0 && !fa_host::env_flag("FA_B200_FORCE_GENERIC") && fa::bwd_tc_eligible(*a);
+  const int parts = a->parts == 0 ? 3 : a->parts;  // bit 0: dot(dO, O) and dQ, bit 1: dK and dV
+  FA_REQUIRE(parts >= 1 && parts <= 3, "parts must be 0 (everything), 1 (preprocess and dQ) or 2 (dK and dV)");
+  FA_REQUIRE(parts == 3 || tc, "a backward pass can only be split in parts on the tensor-core path");
   // the tensor-core path writes dq directly (two kernels: dK / dV per key block, dQ per query block)
-  int rc = fa::bwd_pre(*a, tc ? 0 : 1, st);
+  int rc = (parts & 1) ? fa::bwd_pre(*a, tc ? 0 : 1, st) : 0;
   if (rc) return rc;
   g_last_path = !tc ? "bwd_generic" : (a->head_dim > 128 ? "bwd_wide_tc" : "bwd_tc+bwd_dq_tc");
   if (tc) {
-    if (a->head_dim > 128) return fa::bwd_wide_tc_main(*a, st);  // one pass per output
-    rc = fa::bwd_tc_main(*a, st);
-    if (rc) return rc;
-    return fa::bwd_dq_tc_main(*a, st);
+    if (a->head_dim > 128) return fa::bwd_wide_tc_main(*a, parts, st);  // one pass per output
+    if (parts & 2) rc = fa::bwd_tc_main(*a, st);
+    if (!rc && (parts & 1)) rc = fa::bwd_dq_tc_main(*a, st);
+    return rc;
   }
   if (a->seqlen_k > 0) {
     rc = fa::bwd_generic_main(*a, st);

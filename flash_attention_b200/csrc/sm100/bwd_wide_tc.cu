@@ -554,18 +554,22 @@ int launch_wide(const FaBwdArgs& a, cudaStream_t st) {
 }
 
 template <typename T>
-int run_wide(const FaBwdArgs& a, cudaStream_t st) {
-  int rc = launch_wide<T, PASS_DV>(a, st);
-  if (!rc) rc = launch_wide<T, PASS_DK>(a, st);
-  if (!rc) rc = launch_wide<T, PASS_DQ>(a, st);
+int run_wide(const FaBwdArgs& a, int parts, cudaStream_t st) {
+  int rc = 0;
+  if (parts & 2) {
+    rc = launch_wide<T, PASS_DV>(a, st);
+    if (!rc) rc = launch_wide<T, PASS_DK>(a, st);
+  }
+  if (!rc && (parts & 1)) rc = launch_wide<T, PASS_DQ>(a, st);
   return rc;
 }
 
 }  // namespace
 
-// dV, dK and dQ of a backward pass with 128 < head_dim <= 256 (softmax_d must hold rowsum(dO o O)).
-int bwd_wide_tc_main(const FaBwdArgs& a, cudaStream_t st) {
-  return a.dtype == FA_DTYPE_BF16 ? run_wide<__nv_bfloat16>(a, st) : run_wide<__half>(a, st);
+// dV, dK (parts & 2) and dQ (parts & 1) of a backward pass with 128 < head_dim <= 256 (softmax_d must hold
+// rowsum(dO o O)).
+int bwd_wide_tc_main(const FaBwdArgs& a, int parts, cudaStream_t st) {
+  return a.dtype == FA_DTYPE_BF16 ? run_wide<__nv_bfloat16>(a, parts, st) : run_wide<__half>(a, parts, st);
 }
 
 }  // namespace fa

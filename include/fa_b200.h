@@ -111,6 +111,11 @@ typedef struct FaBwdArgs {
   int32_t accumulate_dkv;
   float* dk_accum;
   float* dv_accum;
+  /* Run only part of the pass (tensor-core path only; no counterpart in the reference): 0 = everything,
+     1 = dot(dO, O) into softmax_d and dQ, 2 = dK and dV (softmax_d must hold the result of an earlier
+     call with 1).  The ring backward uses it to receive the travelling dK / dV accumulators while dQ of
+     the same step is being computed. */
+  int32_t parts;
 } FaBwdArgs;
 
 /* KV-cache decode.  Replaces mha_fwd_kvcache (flash_api.cpp:1038-1279). */

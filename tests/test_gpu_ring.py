@@ -57,15 +57,13 @@ def _worker(rank, world, port, causal, window, out_q, layout="contiguous"):
             errs.append((e, y))
         out_q.put((rank, errs))
     finally:
+        from flash_attention_b200 import ring
+
+        ring.release_graphs()
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("causal,window,layout", [(True, (-1, -1), "contiguous"), (False, (-1, -1), "contiguous"),
-                                                  (False, (300, 0), "contiguous"), (True, (-1, -1), "zigzag")])
-def test_ring_attention_two_gpus(causal, window, layout):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    world = 2
+def _run_ring(world, causal, window, layout):
     ctx = mp.get_context("spawn")
     out_q = ctx.Queue()
     port = _free_port()
@@ -80,6 +78,23 @@ def test_ring_attention_two_gpus(causal, window, layout):
         for e, y in errs:
             # partial outputs are rounded to bf16 once per ring step before the merge
             assert e <= 3 * y + 2e-3, (rank, errs)
+
+
+@pytest.mark.parametrize("causal,window,layout", [(True, (-1, -1), "contiguous"), (False, (-1, -1), "contiguous"),
+                                                  (False, (300, 0), "contiguous"), (True, (-1, -1), "zigzag")])
+def test_ring_attention_two_gpus(causal, window, layout):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _run_ring(2, causal, window, layout)
+
+
+@pytest.mark.parametrize("world", [4, 8])
+@pytest.mark.parametrize("causal,window,layout", [(True, (-1, -1), "zigzag"), (False, (700, 0), "contiguous")])
+def test_ring_attention_more_gpus(world, causal, window, layout):
+    # the balanced causal layout, and a window that ends the ring after two steps (most dK / dV slots stay zero)
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    _run_ring(world, causal, window, layout)
 
 
 @pytest.mark.gpu
@@ -128,8 +143,9 @@ def test_block_backward_adds_dk_dv_into_fp32_accumulators(d):
     out, lse = CudaBlockOps.fwd(q, k, v, scale, (-1, 0), shift)
     dk_acc = torch.zeros(B, Sk, Hk, d, dtype=torch.float32, device="cuda")
     dv_acc = torch.zeros_like(dk_acc)
-    for _ in range(2):
-        dq = CudaBlockOps.bwd(do, q, k, v, out, lse, dk_acc, dv_acc, scale, (-1, 0), shift)
+    # once whole, once as its two halves (dot(dO, O) + dQ, then dK / dV)
+    for parts in (0, (1, 2)):
+        dq = CudaBlockOps.bwd(do, q, k, v, out, lse, dk_acc, dv_acc, scale, (-1, 0), shift, parts=parts)
     torch.cuda.synchronize()
     assert torch.allclose(dq.float(), want_dq.float(), atol=1e-2, rtol=1e-2)
     # the plain call rounds dk / dv to bf16 once; the accumulators keep fp32
