@@ -1,9 +1,16 @@
-"""Rotary position embedding in front of attention: the public functions of the reference's
-flash_attn/layers/rotary.py (apply_rotary_emb :96-124, apply_rotary_emb_qkv_ :207-231,
-apply_rotary_emb_kv_ :271-292, RotaryEmbedding :295-480) with the same arguments and autograd
-behaviour, on top of the `fa_rotary` entry point of the C ABI instead of the Triton kernel
-(flash_attn/ops/triton/rotary.py).  The backward of a rotation is the rotation by the negative
-angle (`conjugate`), so no activations are saved besides the tables.
+"""Rotary position embedding in front of attention.
+
+Public surface (names, arguments, in-place behaviour and gradients) of the reference's
+flash_attn/layers/rotary.py: apply_rotary_emb (:96-124), apply_rotary_emb_qkv_ (:207-231),
+apply_rotary_emb_kv_ (:271-292), RotaryEmbedding (:295-480), plus the attributes that
+flash_attn/modules/mha.py:451-455 reads from the module (scale, _update_cos_sin_cache, _cos_cached,
+_sin_cached).  Underneath it is built differently: `apply_rotary` binds the `fa_rotary` entry point of the
+C ABI (in place of the Triton kernel of flash_attn/ops/triton/rotary.py), ONE autograd node serves every
+entry point -- each of them only says which 4-D views of its tensor turn with which table pair -- and the
+module keeps its tables in a small cache object of its own.
+
+A rotation is orthogonal, so its backward is the rotation by the negative angle (`conjugate`) of the
+incoming gradient: nothing but the tables and the offsets is kept for it.
 """
 import ctypes
 from typing import Optional, Union
@@ -81,191 +88,193 @@ def apply_rotary(x, cos, sin, seqlen_offsets: Union[int, torch.Tensor] = 0, cu_s
     return out
 
 
-class ApplyRotaryEmb(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, x, cos, sin, interleaved=False, inplace=False, seqlen_offsets: Union[int, torch.Tensor] = 0,
-                cu_seqlens: Optional[torch.Tensor] = None, max_seqlen: Optional[int] = None):
-        out = apply_rotary(x, cos, sin, seqlen_offsets=seqlen_offsets, cu_seqlens=cu_seqlens, max_seqlen=max_seqlen,
-                           interleaved=interleaved, inplace=inplace)
-        if isinstance(seqlen_offsets, int):
-            ctx.save_for_backward(cos, sin, cu_seqlens)
-            ctx.seqlen_offsets = seqlen_offsets
-        else:
-            ctx.save_for_backward(cos, sin, cu_seqlens, seqlen_offsets)
-            ctx.seqlen_offsets = None
-        ctx.interleaved, ctx.inplace, ctx.max_seqlen = interleaved, inplace, max_seqlen
-        return out if not inplace else x
+# ------------------------------------------------------------------------------------------------
+# One autograd node for all entry points
+#
+# A "turn list" names what to rotate: pairs (view of the tensor, index of the table pair).  The three public
+# shapes differ only in that list:
+#   x    (batch, seqlen, heads, d)     -> the tensor itself with tables 0
+#   qkv  (batch, seqlen, 3, heads, d)  -> q and k; as ONE view over 2 * heads heads when both use tables 0
+#   kv   (batch, seqlen, 2, heads, d)  -> k
+def _turns_x(t, two_tables):
+    return [(t, 0)]
+
+
+def _turns_qkv(t, two_tables):
+    batch, seqlen, three, heads, d = t.shape
+    if three != 3:
+        raise ValueError("qkv must have shape (batch, seqlen, 3, nheads, headdim)")
+    if not two_tables and t.is_contiguous():
+        return [(t[:, :, :2].reshape(batch, seqlen, 2 * heads, d), 0)]  # q and k heads are neighbours in memory
+    return [(t[:, :, 0], 0), (t[:, :, 1], 1 if two_tables else 0)]
+
+
+def _turns_kv(t, two_tables):
+    if t.shape[2] != 2:
+        raise ValueError("kv must have shape (batch, seqlen, 2, nheads, headdim)")
+    return [(t[:, :, 0], 0)]
+
+
+class _Turn(torch.autograd.Function):
+    """forward(t, turns, opts, offsets, cos, sin, cos_k, sin_k) -> rotated t.
+
+    opts = (interleaved, inplace, cu_seqlens, max_seqlen).  Out of place only for the plain-x entry (the packed
+    entries are in place by contract)."""
 
     @staticmethod
-    def backward(ctx, do):
-        seqlen_offsets = ctx.seqlen_offsets
-        if seqlen_offsets is None:
-            cos, sin, cu_seqlens, seqlen_offsets = ctx.saved_tensors
-        else:
-            cos, sin, cu_seqlens = ctx.saved_tensors
-        dx = apply_rotary(do, cos, sin, seqlen_offsets=seqlen_offsets, cu_seqlens=cu_seqlens, max_seqlen=ctx.max_seqlen,
-                          interleaved=ctx.interleaved, inplace=ctx.inplace and do.stride(-1) == 1, conjugate=True)
-        return dx, None, None, None, None, None, None, None
+    def _run(t, turns, opts, offsets, tables, conjugate, inplace):
+        interleaved, _, cu_seqlens, max_seqlen = opts
+        two = tables[1][0] is not None
+        result = t
+        for view, which in turns(t, two):
+            cos, sin = tables[which]
+            r = apply_rotary(view, cos, sin, seqlen_offsets=offsets, cu_seqlens=cu_seqlens, max_seqlen=max_seqlen,
+                             interleaved=interleaved, inplace=inplace, conjugate=conjugate)
+            if not inplace:
+                result = r  # only the single-view entry gets here
+        return result
+
+    @staticmethod
+    def forward(ctx, t, turns, opts, offsets, cos, sin, cos_k, sin_k):
+        inplace = opts[1]
+        out = _Turn._run(t, turns, opts, offsets, ((cos, sin), (cos_k, sin_k)), False, inplace)
+        ctx.turns, ctx.opts = turns, opts
+        ctx.int_offsets = None if torch.is_tensor(offsets) else offsets
+        ctx.save_for_backward(cos, sin, cos_k, sin_k, offsets if torch.is_tensor(offsets) else None)
+        # an in-place call hands back its own argument (leaves that require grad included), as the reference does
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        cos, sin, cos_k, sin_k, offsets = ctx.saved_tensors
+        if offsets is None:
+            offsets = ctx.int_offsets
+        inplace = ctx.opts[1]
+        if inplace and grad.stride(-1) != 1:
+            grad = grad.contiguous()
+        # an in-place forward lets the gradient be turned in place too: it belongs to this node alone
+        dx = _Turn._run(grad, ctx.turns, ctx.opts, offsets, ((cos, sin), (cos_k, sin_k)), True, inplace)
+        return (dx,) + (None,) * 7
 
 
 def apply_rotary_emb(x, cos, sin, interleaved=False, inplace=False, seqlen_offsets: Union[int, torch.Tensor] = 0,
                      cu_seqlens: Optional[torch.Tensor] = None, max_seqlen: Optional[int] = None):
-    """x: (batch_size, seqlen, nheads, headdim), or (total_seqlen, nheads, headdim) with cu_seqlens.
-    cos, sin: (seqlen_rotary, rotary_dim / 2).  interleaved: rotate pairs of even and odd dimensions
-    (GPT-J style) instead of first and second half (GPT-NeoX style).  seqlen_offsets: int or (batch_size,):
-    shift of every sequence, as used with a KV cache.  Rotates the first rotary_dim of every row."""
-    return ApplyRotaryEmb.apply(x, cos, sin, interleaved, inplace, seqlen_offsets, cu_seqlens, max_seqlen)
+    """Rotates the first rotary_dim of every row of x.
+
+    x: (batch, seqlen, nheads, headdim), or (total_seqlen, nheads, headdim) together with cu_seqlens and
+    max_seqlen.  cos, sin: (seqlen_rotary, rotary_dim / 2).  interleaved: pairs are (even, odd) dimensions
+    (GPT-J) instead of (first half, second half) (GPT-NeoX).  seqlen_offsets: an int, or one int per batch
+    entry: position of each sequence's first row (decoding with a KV cache)."""
+    opts = (bool(interleaved), bool(inplace), cu_seqlens, max_seqlen)
+    return _Turn.apply(x, _turns_x, opts, seqlen_offsets, cos, sin, None, None)
 
 
-apply_rotary_emb_func = apply_rotary_emb  # name kept by the reference for backward compatibility
-
-
-def _rotate_qk_(qkv, cos, sin, cos_k, sin_k, interleaved, seqlen_offsets, conjugate):
-    """In-place rotation of q and k inside a (batch, seqlen, 3, nheads, headdim) tensor."""
-    batch, seqlen, three, nheads, headdim = qkv.shape
-    if cos_k is None and sin_k is None and qkv.is_contiguous():
-        # q and k heads are adjacent in memory: one call over 2 * nheads heads
-        qk = qkv[:, :, :2].reshape(batch, seqlen, -1, headdim)
-        apply_rotary(qk, cos, sin, seqlen_offsets=seqlen_offsets, interleaved=interleaved, inplace=True, conjugate=conjugate)
-    else:
-        cos_k = cos if cos_k is None else cos_k
-        sin_k = sin if sin_k is None else sin_k
-        apply_rotary(qkv[:, :, 0], cos, sin, seqlen_offsets, interleaved=interleaved, inplace=True, conjugate=conjugate)
-        apply_rotary(qkv[:, :, 1], cos_k, sin_k, seqlen_offsets, interleaved=interleaved, inplace=True, conjugate=conjugate)
-
-
-class ApplyRotaryEmbQKV_(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, qkv, cos, sin, cos_k=None, sin_k=None, interleaved=False, seqlen_offsets: Union[int, torch.Tensor] = 0):
-        assert qkv.shape[2] == 3
-        _rotate_qk_(qkv, cos, sin, cos_k, sin_k, interleaved, seqlen_offsets, False)
-        if isinstance(seqlen_offsets, int):
-            ctx.save_for_backward(cos, sin, cos_k, sin_k)
-            ctx.seqlen_offsets = seqlen_offsets
-        else:
-            ctx.save_for_backward(cos, sin, cos_k, sin_k, seqlen_offsets)
-            ctx.seqlen_offsets = None
-        ctx.interleaved = interleaved
-        return qkv
-
-    @staticmethod
-    def backward(ctx, dqkv):
-        seqlen_offsets = ctx.seqlen_offsets
-        if seqlen_offsets is None:
-            cos, sin, cos_k, sin_k, seqlen_offsets = ctx.saved_tensors
-        else:
-            cos, sin, cos_k, sin_k = ctx.saved_tensors
-        if dqkv.stride(-1) != 1:
-            dqkv = dqkv.contiguous()
-        _rotate_qk_(dqkv, cos, sin, cos_k, sin_k, ctx.interleaved, seqlen_offsets, True)
-        return dqkv, None, None, None, None, None, None
+apply_rotary_emb_func = apply_rotary_emb  # the reference keeps this older name too
 
 
 def apply_rotary_emb_qkv_(qkv, cos, sin, cos_k=None, sin_k=None, interleaved=False,
                           seqlen_offsets: Union[int, torch.Tensor] = 0):
-    """qkv: (batch_size, seqlen, 3, nheads, headdim); cos, sin (and optionally cos_k, sin_k for the
-    keys): (seqlen, rotary_dim / 2).  Rotates the first rotary_dim of Q and K *in place*."""
-    return ApplyRotaryEmbQKV_.apply(qkv, cos, sin, cos_k, sin_k, interleaved, seqlen_offsets)
-
-
-class ApplyRotaryEmbKV_(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, kv, cos, sin, interleaved=False, seqlen_offsets: Union[int, torch.Tensor] = 0):
-        assert kv.shape[2] == 2
-        apply_rotary(kv[:, :, 0], cos, sin, seqlen_offsets=seqlen_offsets, interleaved=interleaved, inplace=True)
-        if isinstance(seqlen_offsets, int):
-            ctx.save_for_backward(cos, sin)
-            ctx.seqlen_offsets = seqlen_offsets
-        else:
-            ctx.save_for_backward(cos, sin, seqlen_offsets)
-            ctx.seqlen_offsets = None
-        ctx.interleaved = interleaved
-        return kv
-
-    @staticmethod
-    def backward(ctx, dkv):
-        seqlen_offsets = ctx.seqlen_offsets
-        if seqlen_offsets is None:
-            cos, sin, seqlen_offsets = ctx.saved_tensors
-        else:
-            cos, sin = ctx.saved_tensors
-        if dkv.stride(-1) != 1:
-            dkv = dkv.contiguous()
-        apply_rotary(dkv[:, :, 0], cos, sin, seqlen_offsets=seqlen_offsets, interleaved=ctx.interleaved, inplace=True,
-                     conjugate=True)
-        return dkv, None, None, None, None
+    """In place on q and k of qkv (batch, seqlen, 3, nheads, headdim); returns qkv.  cos_k, sin_k: separate
+    tables for the keys (XPos); the queries' tables serve both when they are None."""
+    if (cos_k is None) != (sin_k is None):
+        raise ValueError("cos_k and sin_k come together")
+    opts = (bool(interleaved), True, None, None)
+    return _Turn.apply(qkv, _turns_qkv, opts, seqlen_offsets, cos, sin, cos_k, sin_k)
 
 
 def apply_rotary_emb_kv_(kv, cos, sin, interleaved=False, seqlen_offsets: Union[int, torch.Tensor] = 0):
-    """kv: (batch_size, seqlen, 2, nheads, headdim).  Rotates the first rotary_dim of K *in place*."""
-    return ApplyRotaryEmbKV_.apply(kv, cos, sin, interleaved, seqlen_offsets)
+    """In place on k of kv (batch, seqlen, 2, nheads, headdim); returns kv."""
+    opts = (bool(interleaved), True, None, None)
+    return _Turn.apply(kv, _turns_kv, opts, seqlen_offsets, cos, sin, None, None)
+
+
+# ------------------------------------------------------------------------------------------------
+# The module: angle tables made on demand
+class _AngleTables:
+    """cos / sin of position x frequency for positions [0, rows), in the activations' dtype, for one device.
+
+    With XPos (`xpos` = (per-pair base, scale_base)) queries and keys get reciprocal magnitudes
+    zeta ** (+-(position - rows // 2) / scale_base), so that their product depends on the distance alone."""
+
+    def __init__(self):
+        self.rows, self.q, self.k = 0, (None, None), (None, None)
+
+    def stale(self, rows, device, dtype, training):
+        c = self.q[0]
+        return (c is None or rows > self.rows or c.device != device or c.dtype != dtype
+                # tables made under torch.inference_mode() cannot enter an autograd graph later
+                or (training and c.is_inference()))
+
+    def build(self, rows, freq, xpos, device, dtype):
+        pos = torch.arange(rows, device=device, dtype=freq.dtype)
+        angle = pos[:, None] * freq[None, :]
+        c, s = angle.cos(), angle.sin()
+        self.rows = rows
+        if xpos is None:
+            self.q, self.k = (c.to(dtype), s.to(dtype)), (None, None)
+            return
+        zeta, scale_base = xpos
+        exponent = (torch.arange(rows, device=zeta.device, dtype=zeta.dtype) - rows // 2) / scale_base
+        mag = (zeta.to(exponent.device)[None, :] ** exponent[:, None]).to(device)
+        self.q = ((c * mag).to(dtype), (s * mag).to(dtype))
+        self.k = ((c / mag).to(dtype), (s / mag).to(dtype))
 
 
 class RotaryEmbedding(torch.nn.Module):
-    """Rotary position embedding with cached cos / sin tables and optional XPos scaling
-    (flash_attn/layers/rotary.py:295-480): forward(qkv, kv=None, seqlen_offset=0, max_seqlen=None)
-    rotates q and k in place, either inside a packed qkv (kv is None) or q in `qkv` and k in `kv`."""
+    """Rotary embedding of q and k in front of attention (RoFormer), optionally with XPos magnitudes.
+
+    RotaryEmbedding(dim, base=10000.0, interleaved=False, scale_base=None, pos_idx_in_fp32=True, device=None);
+    forward(qkv, kv=None, seqlen_offset=0, max_seqlen=None) turns, in place, q and k of a packed
+    (batch, seqlen, 3, nheads, headdim) tensor, or q = `qkv` (batch, seqlen, nheads, headdim) and k inside
+    `kv` (batch, seqlen, 2, nheads_k, headdim), and returns what it was given.  Frequencies are
+    base ** (-2i / dim); with pos_idx_in_fp32 positions and frequencies stay fp32 whatever dtype the module was
+    cast to (bf16 cannot tell position 257 from 256).  The tables grow with the longest sequence seen."""
 
     def __init__(self, dim: int, base=10000.0, interleaved=False, scale_base=None, pos_idx_in_fp32=True, device=None):
         super().__init__()
-        self.dim = dim
-        self.base = float(base)
-        self.pos_idx_in_fp32 = pos_idx_in_fp32
-        self.register_buffer("inv_freq", self._compute_inv_freq(device), persistent=False)
-        self.interleaved = interleaved
-        self.scale_base = scale_base
-        scale = ((torch.arange(0, dim, 2, device=device, dtype=torch.float32) + 0.4 * dim) / (1.4 * dim)
-                 if scale_base is not None else None)
-        self.register_buffer("scale", scale, persistent=False)
-        self._seq_len_cached = 0
-        self._cos_cached = self._sin_cached = self._cos_k_cached = self._sin_k_cached = None
+        self.dim, self.base, self.interleaved = dim, float(base), interleaved
+        self.scale_base, self.pos_idx_in_fp32 = scale_base, pos_idx_in_fp32
+        self.register_buffer("inv_freq", self._frequencies(device), persistent=False)
+        zeta = None
+        if scale_base is not None:
+            pair = torch.arange(0, dim, 2, device=device, dtype=torch.float32)
+            zeta = (pair + 0.4 * dim) / (1.4 * dim)  # XPos: per-pair base in (0.29, 1)
+        self.register_buffer("scale", zeta, persistent=False)
+        self._tables = _AngleTables()
 
-    def _compute_inv_freq(self, device=None):
-        return 1.0 / (self.base ** (torch.arange(0, self.dim, 2, device=device, dtype=torch.float32) / self.dim))
+    def _frequencies(self, device=None):
+        pair = torch.arange(0, self.dim, 2, device=device, dtype=torch.float32)
+        return torch.reciprocal(self.base ** (pair / self.dim))  # rounded like the published tables: 1 / base^(2i/dim)
+
+    # what flash_attn/modules/mha.py reads when it hands the tables to the KV-cache kernel
+    _cos_cached = property(lambda self: self._tables.q[0])
+    _sin_cached = property(lambda self: self._tables.q[1])
+    _cos_k_cached = property(lambda self: self._tables.k[0])
+    _sin_k_cached = property(lambda self: self._tables.k[1])
+    _seq_len_cached = property(lambda self: self._tables.rows)
 
     def _update_cos_sin_cache(self, seqlen, device=None, dtype=None):
-        # rebuilt when the sequence grows, the device or dtype changes, or the cache was made under inference mode
-        if (seqlen > self._seq_len_cached or self._cos_cached is None or self._cos_cached.device != device
-                or self._cos_cached.dtype != dtype or (self.training and self._cos_cached.is_inference())):
-            self._seq_len_cached = seqlen
-            if self.pos_idx_in_fp32:
-                # positions and frequencies in fp32: bf16 positions would collide past 256
-                t = torch.arange(seqlen, device=device, dtype=torch.float32)
-                inv_freq = self.inv_freq if self.inv_freq.dtype == torch.float32 else self._compute_inv_freq(device=device)
-            else:
-                t = torch.arange(seqlen, device=device, dtype=self.inv_freq.dtype)
-                inv_freq = self.inv_freq
-            freqs = torch.outer(t, inv_freq)
-            if self.scale is None:
-                self._cos_cached = torch.cos(freqs).to(dtype)
-                self._sin_cached = torch.sin(freqs).to(dtype)
-            else:
-                power = (torch.arange(seqlen, dtype=self.scale.dtype, device=self.scale.device) - seqlen // 2) / self.scale_base
-                scale = self.scale.to(device=power.device) ** power.unsqueeze(-1)
-                self._cos_cached = (torch.cos(freqs) * scale).to(dtype)
-                self._sin_cached = (torch.sin(freqs) * scale).to(dtype)
-                self._cos_k_cached = (torch.cos(freqs) / scale).to(dtype)
-                self._sin_k_cached = (torch.sin(freqs) / scale).to(dtype)
+        if not self._tables.stale(seqlen, device, dtype, self.training):
+            return
+        freq = self.inv_freq
+        if self.pos_idx_in_fp32 and freq.dtype != torch.float32:
+            freq = self._frequencies(device)  # the buffer was cast with the module; take the exact values again
+        xpos = None if self.scale is None else (self.scale, self.scale_base)
+        self._tables.build(seqlen, freq.to(device), xpos, device, dtype)
 
     def forward(self, qkv: torch.Tensor, kv: Optional[torch.Tensor] = None, seqlen_offset: Union[int, torch.Tensor] = 0,
                 max_seqlen: Optional[int] = None):
-        seqlen = qkv.shape[1]
+        """seqlen_offset: int, or one int per batch entry (then pass max_seqlen, the longest position + 1 that
+        can occur, so the tables can be sized without reading the tensor back)."""
         if max_seqlen is not None:
             self._update_cos_sin_cache(max_seqlen, device=qkv.device, dtype=qkv.dtype)
         elif isinstance(seqlen_offset, int):
-            self._update_cos_sin_cache(seqlen + seqlen_offset, device=qkv.device, dtype=qkv.dtype)
+            self._update_cos_sin_cache(qkv.shape[1] + seqlen_offset, device=qkv.device, dtype=qkv.dtype)
+        (cq, sq), (ck, sk) = self._tables.q, self._tables.k
+        how = dict(interleaved=self.interleaved, seqlen_offsets=seqlen_offset)
         if kv is None:
-            if self.scale is None:
-                return apply_rotary_emb_qkv_(qkv, self._cos_cached, self._sin_cached, interleaved=self.interleaved,
-                                             seqlen_offsets=seqlen_offset)
-            return apply_rotary_emb_qkv_(qkv, self._cos_cached, self._sin_cached, self._cos_k_cached, self._sin_k_cached,
-                                         interleaved=self.interleaved, seqlen_offsets=seqlen_offset)
-        q = apply_rotary_emb_func(qkv, self._cos_cached, self._sin_cached, interleaved=self.interleaved, inplace=True,
-                                  seqlen_offsets=seqlen_offset)
-        if self.scale is None:
-            kv = apply_rotary_emb_kv_(kv, self._cos_cached, self._sin_cached, interleaved=self.interleaved,
-                                      seqlen_offsets=seqlen_offset)
-        else:
-            kv = apply_rotary_emb_kv_(kv, self._cos_k_cached, self._sin_k_cached, interleaved=self.interleaved,
-                                      seqlen_offsets=seqlen_offset)
-        return q, kv
+            return apply_rotary_emb_qkv_(qkv, cq, sq, ck, sk, **how)
+        q = apply_rotary_emb(qkv, cq, sq, inplace=True, **how)
+        if ck is None:
+            ck, sk = cq, sq
+        return q, apply_rotary_emb_kv_(kv, ck, sk, **how)

@@ -200,3 +200,51 @@ def test_rotary_embedding_module_matches_function_and_attention_runs_on_it():
     q, kv = rot_x(qkv[:, :, 0].clone(), qkv[:, :, 1:].clone(), seqlen_offset=5)
     assert q.shape == (B, S, H, D) and kv.shape == (B, S, 2, H, D)
     assert torch.equal(kv[:, :, 1], qkv[:, :, 2])
+
+
+def test_unmodified_reference_rotary_layer_on_this_kernel(monkeypatch):
+    """The reference's own flash_attn/layers/rotary.py, loaded as it is, with the one symbol it imports
+    (apply_rotary of its Triton module) supplied by this repository's CUDA binding: module forward and
+    backward against the oracle, and bit-equal to this repository's own layer."""
+    import importlib.util
+    import os
+    import sys
+    import types
+
+    from flash_attention_b200.layers import rotary as mine
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = None
+    for r in (os.environ.get("FLASH_ATTN_REFERENCE_TREE"), os.path.join(root, "baseline", "_ref")):
+        if r and os.path.exists(os.path.join(r, "flash_attn", "layers", "rotary.py")):
+            path = os.path.join(r, "flash_attn", "layers", "rotary.py")
+            break
+    if path is None:
+        pytest.skip("no copy of the reference's flash_attn package on this machine")
+    for name in ("flash_attn", "flash_attn.ops", "flash_attn.ops.triton"):
+        if name not in sys.modules:
+            monkeypatch.setitem(sys.modules, name, types.ModuleType(name))
+    stub = types.ModuleType("flash_attn.ops.triton.rotary")
+    stub.apply_rotary = mine.apply_rotary
+    monkeypatch.setitem(sys.modules, "flash_attn.ops.triton.rotary", stub)
+    spec = importlib.util.spec_from_file_location("reference_layers_rotary", path)
+    theirs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(theirs)
+
+    g = torch.Generator().manual_seed(49)
+    B, S, H, D, off = 3, 257, 6, 128, 11
+    qkv = torch.randn(B, S, 3, H, D, generator=g).bfloat16().cuda()
+    do = torch.randn(B, S, 3, H, D, generator=g).bfloat16().cuda()
+    for interleaved in (False, True):
+        a = mine.RotaryEmbedding(D, interleaved=interleaved, device="cuda")
+        b = theirs.RotaryEmbedding(D, interleaved=interleaved, device="cuda")
+        xa, xb = qkv.clone().requires_grad_(), qkv.clone().requires_grad_()
+        ya, yb = a(xa, seqlen_offset=off), b(xb, seqlen_offset=off)
+        cos, sin = b._cos_cached, b._sin_cached
+        _close(yb[:, :, 0].detach(), _expected(qkv[:, :, 0], cos, sin, off, interleaved))
+        _close(yb[:, :, 1].detach(), _expected(qkv[:, :, 1], cos, sin, off, interleaved))
+        assert torch.equal(ya, yb)
+        ya.backward(do.clone())
+        yb.backward(do.clone())
+        _close(xb.grad[:, :, 1], _expected(do[:, :, 1], cos, -sin, off, interleaved))
+        assert torch.equal(xa.grad, xb.grad)
