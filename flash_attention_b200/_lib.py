@@ -41,6 +41,7 @@ class FaFwdArgs(C.Structure):
         ("num_splits", c_i32),
         ("lse_accum", c_vp), ("out_accum", c_vp),
         ("use_mask_shift", c_i32), ("mask_shift", c_i32),
+        ("block_table", c_vp), ("block_table_stride", c_i32), ("page_block_size", c_i32),
     ]
 
 
@@ -66,6 +67,7 @@ class FaBwdArgs(C.Structure):
         ("accumulate_dkv", c_i32),
         ("dk_accum", c_vp), ("dv_accum", c_vp),
         ("parts", c_i32),
+        ("deterministic", c_i32),
     ]
 
 
@@ -86,6 +88,7 @@ class FaKvcacheArgs(C.Structure):
         ("num_splits", c_i32),
         ("lse_accum", c_vp), ("out_accum", c_vp),
         ("q_rotated", c_vp),
+        ("block_table", c_vp), ("block_table_stride", c_i32), ("page_block_size", c_i32),
     ]
 
 

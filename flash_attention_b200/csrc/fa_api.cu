@@ -220,6 +220,14 @@ int fa_fwd(const FaFwdArgs* a, fa_stream_t stream) {
     FA_REQUIRE(!a->cu_seqlens_q, "split-KV is not available for packed variable-length input");
     FA_REQUIRE(a->p_dropout == 0.f, "split-KV does not support dropout");
   }
+  if (a->block_table) {
+    FA_REQUIRE(a->page_block_size > 0 && a->page_block_size % 64 == 0, "Paged KV cache block size must be divisible by 64");
+    FA_REQUIRE(a->block_table_stride > 0 &&
+                   (int64_t)a->block_table_stride * a->page_block_size >= a->seqlen_k,
+               "a row of block_table must cover seqlen_k keys");
+    FA_REQUIRE(!a->cu_seqlens_k && !a->kv_batch_idx && !a->s_dmask,
+               "paged K/V is not combined with cu_seqlens_k, kv_batch_idx or a returned probability matrix");
+  }
   if (a->seqlen_q == 0 || a->batch == 0) return 0;
   if (refuse_if_device_failed()) return 3;
   int rc;
@@ -294,8 +302,15 @@ static int kvcache_checks(const FaKvcacheArgs* a) {
     FA_REQUIRE(a->rotary_dim % 16 == 0, "Only rotary dimensions divisible by 16 are currently supported");
     FA_REQUIRE(a->seqlen_ro >= a->seqlen_cache, "cos/sin seqlen must be at least the seqlen of KV cache");
   }
-  if (!a->cache_batch_idx)
+  if (a->block_table) {
+    FA_REQUIRE(a->cache_batch_idx == nullptr, "Paged KVcache does not support cache_batch_idx");
+    FA_REQUIRE(a->page_block_size > 0 && a->page_block_size % 64 == 0, "Paged KV cache block size must be divisible by 64");
+    FA_REQUIRE(a->block_table_stride > 0 && a->seqlen_cache % a->page_block_size == 0 &&
+                   a->seqlen_cache / a->page_block_size <= a->block_table_stride,
+               "seqlen_cache must be (pages per sequence) * page_block_size, within one row of block_table");
+  } else if (!a->cache_batch_idx) {
     FA_REQUIRE(a->batch_cache >= a->batch, "the KV cache holds fewer sequences than q");
+  }
   return 0;
 }
 
@@ -366,6 +381,9 @@ int fa_fwd_kvcache(const FaKvcacheArgs* a, fa_stream_t stream) {
   f.seqused_k = a->cache_seqlens;
   f.seqused_k_extra = a->knew.ptr ? a->seqlen_new : 0;
   f.kv_batch_idx = a->cache_batch_idx;
+  f.block_table = a->block_table;
+  f.block_table_stride = a->block_table_stride;
+  f.page_block_size = a->page_block_size;
   f.num_splits = splits;
   f.lse_accum = a->lse_accum;
   f.out_accum = a->out_accum;

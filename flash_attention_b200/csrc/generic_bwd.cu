@@ -110,7 +110,7 @@ __device__ __forceinline__ void load_tile_64b(T* s, const T* g, int64_t row_stri
 // DP: padded head dim contracted over (64/128/256); DA = min(DP,128): columns of dK/dV/dQ that
 // this CTA owns (column part = blockIdx.x % (DP/DA)).
 template <typename T, int DP>
-__global__ void __launch_bounds__(128) bwd_generic_kernel(const __grid_constant__ FaBwdArgs p) {
+__global__ void __launch_bounds__(128) bwd_generic_kernel(const __grid_constant__ FaBwdArgs p, const int nblk0) {
   constexpr int DA = DP > 128 ? 128 : DP;
   constexpr int NPART = DP / DA;
   constexpr int LD = DP + 8;
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(128) bwd_generic_kernel(const __grid_constant_
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int part = blockIdx.x % NPART;
-  const int nblk = blockIdx.x / NPART;
+  const int nblk = nblk0 + blockIdx.x / NPART;
   const int hk = blockIdx.y, b = blockIdx.z;
   const int group = p.heads / p.heads_k;
   const SeqInfo si = seq_info(p.cu_seqlens_q, p.cu_seqlens_k, nullptr, nullptr, p.seqlen_q, p.seqlen_k,
@@ -339,8 +339,19 @@ static int launch_bwd_generic(const FaBwdArgs& a, cudaStream_t st) {
   auto kern = bwd_generic_kernel<T, DP>;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   constexpr int NPART = DP > 128 ? DP / 128 : 1;
-  dim3 grid(((a.seqlen_k + 63) / 64) * NPART, a.heads_k, a.batch);
-  kern<<<grid, 128, smem, st>>>(a);
+  const int nblocks = (a.seqlen_k + 63) / 64;
+  if (a.deterministic) {
+    // One launch per key block: inside a launch no two CTAs add into the same dq value (they own different
+    // batch entries, heads or column parts), and the stream orders the launches, so every dq value receives
+    // its terms in key order.
+    for (int nb = 0; nb < nblocks; ++nb) {
+      kern<<<dim3(NPART, a.heads_k, a.batch), 128, smem, st>>>(a, nb);
+      if (int rc = fa_host::check_launch("bwd_generic_kernel")) return rc;
+    }
+    return 0;
+  }
+  dim3 grid(nblocks * NPART, a.heads_k, a.batch);
+  kern<<<grid, 128, smem, st>>>(a, 0);
   return fa_host::check_launch("bwd_generic_kernel");
 }
 

@@ -47,9 +47,10 @@ __global__ void __launch_bounds__(128) fwd_generic_kernel(const __grid_constant_
   const int D = p.head_dim;
   const T* qg = reinterpret_cast<const T*>(p.q.ptr) + si.q_batch * p.q.stride_b + si.q_row0 * p.q.stride_s +
                 (int64_t)h * p.q.stride_h;
-  const T* kg = reinterpret_cast<const T*>(p.k.ptr) + si.k_batch * p.k.stride_b + si.k_row0 * p.k.stride_s +
+  const int64_t kbatch = p.block_table ? 0 : si.k_batch;  // paged: the page offset is added per tile
+  const T* kg = reinterpret_cast<const T*>(p.k.ptr) + kbatch * p.k.stride_b + si.k_row0 * p.k.stride_s +
                 (int64_t)hk * p.k.stride_h;
-  const T* vg = reinterpret_cast<const T*>(p.v.ptr) + si.k_batch * p.v.stride_b + si.k_row0 * p.v.stride_s +
+  const T* vg = reinterpret_cast<const T*>(p.v.ptr) + kbatch * p.v.stride_b + si.k_row0 * p.v.stride_s +
                 (int64_t)hk * p.v.stride_h;
 
   int n_lo, n_hi;
@@ -77,8 +78,16 @@ __global__ void __launch_bounds__(128) fwd_generic_kernel(const __grid_constant_
   for (int n = n_lo; n < n_hi; ++n) {
     const int n0 = n * GF_BN;
     __syncthreads();  // previous tile fully consumed (and sQ visible on the first pass)
-    load_tile_64<T, DP>(sK, kg, p.k.stride_s, n0, si.sk, D, tid);
-    load_tile_64<T, DP>(sV, vg, p.v.stride_s, n0, si.sk, D, tid);
+    if (p.block_table) {
+      // a 64-key tile never straddles a page (page_block_size % 64 == 0): rebase on the page the table names
+      const int64_t page = p.block_table[(int64_t)b * p.block_table_stride + n0 / p.page_block_size];
+      const int r0 = n0 % p.page_block_size;
+      load_tile_64<T, DP>(sK, kg + page * p.k.stride_b, p.k.stride_s, r0, r0 + (si.sk - n0), D, tid);
+      load_tile_64<T, DP>(sV, vg + page * p.v.stride_b, p.v.stride_s, r0, r0 + (si.sk - n0), D, tid);
+    } else {
+      load_tile_64<T, DP>(sK, kg, p.k.stride_s, n0, si.sk, D, tid);
+      load_tile_64<T, DP>(sV, vg, p.v.stride_s, n0, si.sk, D, tid);
+    }
     __syncthreads();
 
     float s[8][4];

@@ -52,11 +52,16 @@ __global__ void __launch_bounds__(128) kvcache_prep_kernel(const __grid_constant
     if (hh >= p.heads_k || !p.knew.ptr) return;
     const int pos = L + r;
     if (pos >= p.seqlen_cache) return;
-    const int cb = p.cache_batch_idx ? p.cache_batch_idx[b] : b;
+    int64_t cb = p.cache_batch_idx ? p.cache_batch_idx[b] : b;
+    int row = pos;
+    if (p.block_table) {  // paged cache: the table names the page, the row is the position inside it
+      cb = p.block_table[(int64_t)b * p.block_table_stride + pos / p.page_block_size];
+      row = pos % p.page_block_size;
+    }
     const T* ks = reinterpret_cast<const T*>(p.knew.ptr) + b * p.knew.stride_b + r * p.knew.stride_s + hh * p.knew.stride_h;
     const T* vs = reinterpret_cast<const T*>(p.vnew.ptr) + b * p.vnew.stride_b + r * p.vnew.stride_s + hh * p.vnew.stride_h;
-    T* kd = reinterpret_cast<T*>(p.kcache.ptr) + cb * p.kcache.stride_b + (int64_t)pos * p.kcache.stride_s + hh * p.kcache.stride_h;
-    T* vd = reinterpret_cast<T*>(p.vcache.ptr) + cb * p.vcache.stride_b + (int64_t)pos * p.vcache.stride_s + hh * p.vcache.stride_h;
+    T* kd = reinterpret_cast<T*>(p.kcache.ptr) + cb * p.kcache.stride_b + (int64_t)row * p.kcache.stride_s + hh * p.kcache.stride_h;
+    T* vd = reinterpret_cast<T*>(p.vcache.ptr) + cb * p.vcache.stride_b + (int64_t)row * p.vcache.stride_s + hh * p.vcache.stride_h;
     const bool rot = cosb != nullptr && pos < p.seqlen_ro;
     rotate_row<T>(ks, kd, rot ? cosb + (int64_t)pos * half : nullptr, rot ? sinb + (int64_t)pos * half : nullptr, D,
                   p.rotary_dim, p.rotary_interleaved != 0, blockDim.x, threadIdx.x);

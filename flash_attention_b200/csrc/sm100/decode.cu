@@ -13,6 +13,8 @@
 // merged at the end), warp 4 = TMA producer.  Q.K^T and P.V use warp-level mma.sync m16n8k16 —
 // 4 useful rows of 16, irrelevant next to the memory time — fed by ldmatrix from the 128B-swizzled
 // tiles that TMA wrote.
+// Paged cache (block_table): the same two tensor maps then describe (page, row in page, head, dim), and the
+// producer looks the page of each 64-key tile up in the table; nothing else changes.
 // New token: the CTA whose key range contains position L = cache_seqlens[b] rotates k_new at L,
 // writes it and v_new to the cache in global memory AND patches them into its shared-memory tile,
 // so no CTA reads a row of global memory that this launch writes.
@@ -145,6 +147,8 @@ __global__ void __launch_bounds__(160, 2) decode_kernel(const __grid_constant__ 
   const bool has_new = a.knew.ptr != nullptr;
   const int Ltot = min(L + (has_new ? 1 : 0), a.seqlen_cache);
   const int cb = a.cache_batch_idx ? a.cache_batch_idx[b] : b;
+  // paged cache: the tensor maps describe (page, row in page); a 64-key tile never straddles a page
+  const int32_t* pages = a.block_table ? a.block_table + (int64_t)b * a.block_table_stride : nullptr;
   const int key_lo = split * P.keys_per_split;
   const int key_hi = min(key_lo + P.keys_per_split, Ltot);
   const int nsplit = P.num_splits;
@@ -211,9 +215,11 @@ __global__ void __launch_bounds__(160, 2) decode_kernel(const __grid_constant__ 
         const uint32_t dst = s_base + slot * C::STAGE_BYTES;
         mbar_expect_tx(bar_full(slot), C::STAGE_BYTES);
         const int key0 = key_lo + i * kTileKeys;
-        for (int c = 0; c < C::NBOX; ++c) tma_load_4d(dst + c * C::BOX_BYTES, &P.tk, bar_full(slot), c * 64, key0, hk, cb);
+        const int row0 = pages ? key0 % a.page_block_size : key0;
+        const int slab = pages ? pages[key0 / a.page_block_size] : cb;
+        for (int c = 0; c < C::NBOX; ++c) tma_load_4d(dst + c * C::BOX_BYTES, &P.tk, bar_full(slot), c * 64, row0, hk, slab);
         for (int c = 0; c < C::NBOX; ++c)
-          tma_load_4d(dst + C::TILE_BYTES + c * C::BOX_BYTES, &P.tv, bar_full(slot), c * 64, key0, hk, cb);
+          tma_load_4d(dst + C::TILE_BYTES + c * C::BOX_BYTES, &P.tv, bar_full(slot), c * 64, row0, hk, slab);
       }
     }
     return;
@@ -257,8 +263,10 @@ __global__ void __launch_bounds__(160, 2) decode_kernel(const __grid_constant__ 
         const int r = L - key0;
         const T* kn = reinterpret_cast<const T*>(a.knew.ptr) + b * a.knew.stride_b + hk * a.knew.stride_h;
         const T* vn = reinterpret_cast<const T*>(a.vnew.ptr) + b * a.vnew.stride_b + hk * a.vnew.stride_h;
-        T* kg = reinterpret_cast<T*>(a.kcache.ptr) + cb * a.kcache.stride_b + (int64_t)L * a.kcache.stride_s + hk * a.kcache.stride_h;
-        T* vg = reinterpret_cast<T*>(a.vcache.ptr) + cb * a.vcache.stride_b + (int64_t)L * a.vcache.stride_s + hk * a.vcache.stride_h;
+        const int64_t slab = pages ? pages[L / a.page_block_size] : cb;
+        const int64_t srow = pages ? L % a.page_block_size : L;
+        T* kg = reinterpret_cast<T*>(a.kcache.ptr) + slab * a.kcache.stride_b + srow * a.kcache.stride_s + hk * a.kcache.stride_h;
+        T* vg = reinterpret_cast<T*>(a.vcache.ptr) + slab * a.vcache.stride_b + srow * a.vcache.stride_s + hk * a.vcache.stride_h;
         for (int c = tid; c < 2 * (D / 8); c += 128) {
           const bool is_v = c >= D / 8;
           const int d0 = (is_v ? c - D / 8 : c) * 8;
@@ -416,8 +424,9 @@ int launch_decode(const FaKvcacheArgs& a, int num_splits, int keys_per_split, cu
   P.a = a;
   P.num_splits = num_splits;
   P.keys_per_split = keys_per_split;
-  if (make_tmap_4d(&P.tk, a.kcache, a.dtype, a.seqlen_cache, a.heads_k, a.batch_cache, a.head_dim, kTileKeys)) return 1;
-  if (make_tmap_4d(&P.tv, a.vcache, a.dtype, a.seqlen_cache, a.heads_k, a.batch_cache, a.head_dim, kTileKeys)) return 1;
+  const int slab_rows = a.block_table ? a.page_block_size : a.seqlen_cache;  // rows of one page / of one sequence's cache
+  if (make_tmap_4d(&P.tk, a.kcache, a.dtype, slab_rows, a.heads_k, a.batch_cache, a.head_dim, kTileKeys)) return 1;
+  if (make_tmap_4d(&P.tv, a.vcache, a.dtype, slab_rows, a.heads_k, a.batch_cache, a.head_dim, kTileKeys)) return 1;
   auto kern = decode_kernel<T, D>;
   P.status = status_ref(may_allocate);
   static fa_host::DeviceOnce once;

@@ -567,7 +567,7 @@ int launch_fwd_tc(const FaFwdArgs& a, cudaStream_t st) {
 bool fwd_tc_eligible(const FaFwdArgs& a) {
   if (a.head_dim > 256 || a.p_dropout > 0.f || a.s_dmask) return false;
   if (a.num_splits > 1 && a.cu_seqlens_q) return false;
-  if (a.seqused_k || a.kv_batch_idx) return false;
+  if (a.seqused_k || a.kv_batch_idx || a.block_table) return false;
   if (a.seqlen_k <= 0) return false;
   if (!tma_compatible(a.q) || !tma_compatible(a.k) || !tma_compatible(a.v)) return false;
   if ((reinterpret_cast<uintptr_t>(a.out.ptr) & 15) || a.out.stride_s % 8 || a.out.stride_h % 8 || a.out.stride_b % 8)

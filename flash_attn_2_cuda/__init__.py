@@ -287,7 +287,7 @@ def _grad_out(given, shape, like, name):
 
 
 def _bwd_common(varlen, dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, cu_q, cu_k, max_q, max_k, p_dropout,
-                softmax_scale, is_causal, wl_in, wr_in, rng_state, what):
+                softmax_scale, is_causal, wl_in, wr_in, rng_state, what, deterministic=False):
     dt = _dtype_code(q)
     _require(k.dtype == q.dtype, "query and key must have the same dtype")
     _require(v.dtype == q.dtype, "query and value must have the same dtype")
@@ -354,6 +354,7 @@ def _bwd_common(varlen, dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, cu_q, cu
             if varlen:
                 a.cu_seqlens_q, a.cu_seqlens_k, a.total_q, a.total_k = ptr(cu_q), ptr(cu_k), total_q, total_k
             a.p_dropout, a.rng_seed, a.rng_offset = float(p_dropout), seed, offset
+            a.deterministic = 1 if deterministic else 0
             check(lib().fa_bwd(ctypes.byref(a), _stream(q)), what)
             del dq_accum
         else:
@@ -374,14 +375,18 @@ def _bwd_common(varlen, dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, cu_q, cu
 
 
 def bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, p_dropout, softmax_scale, is_causal, window_size_left,
-        window_size_right, gen_, rng_state):
-    """mha_bwd (csrc/flash_attn/flash_api.cpp:609-811). Returns [dq, dk, dv, softmax_d]."""
+        window_size_right, gen_, rng_state, *, deterministic=False):
+    """mha_bwd (csrc/flash_attn/flash_api.cpp:609-811). Returns [dq, dk, dv, softmax_d].
+    deterministic (keyword only, not in this version of the reference): dq bit-reproducible from run to run
+    also when the call takes the any-shape kernel (the tensor-core kernels always are)."""
     return _bwd_common(False, dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, None, None, 0, 0, p_dropout,
-                       softmax_scale, is_causal, window_size_left, window_size_right, rng_state, "flash_attn_2_cuda.bwd")
+                       softmax_scale, is_causal, window_size_left, window_size_right, rng_state, "flash_attn_2_cuda.bwd",
+                       deterministic)
 
 
 def varlen_bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-               p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left, window_size_right, gen_, rng_state):
+               p_dropout, softmax_scale, zero_tensors, is_causal, window_size_left, window_size_right, gen_, rng_state,
+               *, deterministic=False):
     """mha_varlen_bwd (csrc/flash_attn/flash_api.cpp:813-1036). Returns [dq, dk, dv, softmax_d]."""
     if zero_tensors:
         for t in (dq_, dk_, dv_):
@@ -389,16 +394,21 @@ def varlen_bwd(dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, cu_seqlens_q, cu_
                 t.zero_()
     return _bwd_common(True, dout, q, k, v, out, softmax_lse, dq_, dk_, dv_, cu_seqlens_q, cu_seqlens_k, max_seqlen_q,
                        max_seqlen_k, p_dropout, softmax_scale, is_causal, window_size_left, window_size_right,
-                       rng_state, "flash_attn_2_cuda.varlen_bwd")
+                       rng_state, "flash_attn_2_cuda.varlen_bwd", deterministic)
 
 
 # -------------------------------------------------------------------------------------------
 def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_, cache_batch_idx_, out_,
-                softmax_scale, is_causal, window_size_left, window_size_right, is_rotary_interleaved, num_splits):
+                softmax_scale, is_causal, window_size_left, window_size_right, is_rotary_interleaved, num_splits,
+                *, block_table=None):
     """mha_fwd_kvcache (csrc/flash_attn/flash_api.cpp:1038-1279). Returns [out, softmax_lse].
 
     kcache / vcache are updated in place at rows [seqlens_k[b], seqlens_k[b] + seqlen_new) of batch
     slot cache_batch_idx[b] when k_ / v_ are given.
+
+    block_table (keyword only; not in this version of the reference, whose 16 positional arguments are kept):
+    (batch, pages_per_sequence) int32.  kcache / vcache are then pools (num_pages, page_block_size, heads_k, d);
+    key j of sequence b is row j % page_block_size of page block_table[b, j // page_block_size].
     """
     dt = _dtype_code(q)
     _require(kcache.dtype == q.dtype, "query and key must have the same dtype")
@@ -407,6 +417,16 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
     _check_last_contig(q, kcache, vcache)
     batch, seqlen_q, heads, d_og = q.shape
     batch_c, seqlen_k, heads_k = kcache.shape[0], kcache.shape[1], kcache.shape[2]
+    page_block_size = 0
+    if block_table is not None:
+        _check_device(block_table)
+        _require(block_table.dtype == torch.int32, "block_table must have dtype torch.int32")
+        _require(block_table.dim() == 2 and block_table.shape[0] == batch and block_table.stride(-1) == 1,
+                 "block_table must have shape (batch, pages per sequence) with contiguous last dimension")
+        _require(cache_batch_idx_ is None, "Paged KVcache does not support cache_batch_idx")
+        page_block_size = seqlen_k  # kcache is (num_pages, page_block_size, heads_k, d)
+        _require(page_block_size % 64 == 0, "Paged KV cache block size must be divisible by 64")
+        seqlen_k = block_table.shape[1] * page_block_size  # capacity of one sequence
     _require(batch > 0, "batch size must be postive")
     _require(d_og <= 256, "FlashAttention forward only supports head dimension at most 256")
     _require(heads % heads_k == 0, "Number of heads in key/value must divide number of heads in query")
@@ -420,8 +440,8 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
         q = q.reshape(batch, heads_k, g, d_og).transpose(1, 2)
         seqlen_q, heads = g, heads_k
     _check_shape(q, batch, seqlen_q, heads, d_og)
-    _check_shape(kcache, batch_c, seqlen_k, heads_k, d_og)
-    _check_shape(vcache, batch_c, seqlen_k, heads_k, d_og)
+    _check_shape(kcache, batch_c, page_block_size or seqlen_k, heads_k, d_og)
+    _check_shape(vcache, batch_c, page_block_size or seqlen_k, heads_k, d_og)
 
     padded = d_og % 8 != 0
     q_p = _aligned(_pad8(q))
@@ -481,7 +501,7 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
         _require(cache_batch_idx_.dtype == torch.int32, "cache_batch_idx must have dtype int32")
         _require(cache_batch_idx_.is_contiguous(), "cache_batch_idx must be contiguous")
         _check_shape(cache_batch_idx_, batch)
-    else:
+    elif block_table is None:
         _require(batch_c >= batch, "the KV cache must hold at least `batch` sequences when cache_batch_idx is not given")
     _require(num_splits <= 128, "num_splits > 128 not supported")
 
@@ -496,6 +516,8 @@ def fwd_kvcache(q, kcache, vcache, k_, v_, seqlens_k_, rotary_cos_, rotary_sin_,
         a.cache_seqlens, a.cache_batch_idx = ptr(seqlens_k_), ptr(cache_batch_idx_)
         a.q_rows_share_position = 1 if swapped else 0
         a.num_splits = int(num_splits)
+        if block_table is not None:
+            a.block_table, a.block_table_stride, a.page_block_size = ptr(block_table), block_table.stride(0), page_block_size
         lse_b, out_b = ctypes.c_int64(0), ctypes.c_int64(0)
         ns = lib().fa_kvcache_plan(ctypes.byref(a), _sm_count(q.device), ctypes.byref(lse_b), ctypes.byref(out_b))
         if ns < 0:

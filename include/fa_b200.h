@@ -81,6 +81,15 @@ typedef struct FaFwdArgs {
      the reference has no ring attention). */
   int32_t use_mask_shift;
   int32_t mask_shift;
+  /* Paged K/V (no counterpart in this version of the reference; the nearest thing is the kv_batch_idx
+     gather of flash_api.cpp:1234-1240).  When block_table != NULL, k / v are pools of pages
+     (num_pages, page_block_size, heads_k, head_dim) addressed with stride_b = page pitch, and key j of
+     sequence b lives in row j % page_block_size of page block_table[b * block_table_stride +
+     j / page_block_size].  page_block_size must be a multiple of 64; not combined with cu_seqlens_k,
+     kv_batch_idx or s_dmask.  Such a call runs on the any-shape kernel. */
+  const int32_t* block_table;
+  int32_t block_table_stride;
+  int32_t page_block_size;
 } FaFwdArgs;
 
 /* Backward.  Replaces mha_bwd (flash_api.cpp:609-811) and mha_varlen_bwd (flash_api.cpp:813-1036),
@@ -116,6 +125,11 @@ typedef struct FaBwdArgs {
      call with 1).  The ring backward uses it to receive the travelling dK / dV accumulators while dQ of
      the same step is being computed. */
   int32_t parts;
+  /* != 0: dq must be bit-reproducible from run to run.  The tensor-core kernels always are (nothing is
+     accumulated atomically).  The any-shape kernel adds its dq tiles into dq_accum with fp32 atomics,
+     one key block per CTA; with this flag it is launched once per key block, so that every dq value
+     receives its terms in key order (slower: seqlen_k / 64 launches). */
+  int32_t deterministic;
 } FaBwdArgs;
 
 /* KV-cache decode.  Replaces mha_fwd_kvcache (flash_api.cpp:1038-1279). */
@@ -140,6 +154,15 @@ typedef struct FaKvcacheArgs {
   float* lse_accum;
   float* out_accum;
   void* q_rotated;                /* scratch for rotated q when the generic path is taken, or NULL */
+  /* Paged cache: block_table != NULL makes kcache / vcache pools of pages (batch_cache = number of pages,
+     page_block_size rows each, stride_b = page pitch); key j of sequence b is row j % page_block_size of
+     page block_table[b * block_table_stride + j / page_block_size]; seqlen_cache is then the capacity
+     per sequence, (entries per row of the table) * page_block_size.  page_block_size % 64 == 0;
+     cache_batch_idx must be NULL.  The fused decode kernel fetches one TMA box per 64 keys from the
+     page the table names; new tokens are appended through the table as well. */
+  const int32_t* block_table;
+  int32_t block_table_stride;
+  int32_t page_block_size;
 } FaKvcacheArgs;
 
 /* flash_attn_2_cuda.fwd / varlen_fwd */

@@ -110,8 +110,15 @@ def test_dropin_module_has_the_reference_entry_points():
     assert os.path.dirname(os.path.abspath(ext.__file__)).startswith(ROOT), "an unrelated flash_attn_2_cuda shadows the shim"
     # positional arities of csrc/flash_attn/flash_api.cpp:248-259, 426-442, 609-625, 813-834, 1038-1055
     want = {"fwd": 11, "varlen_fwd": 16, "bwd": 16, "varlen_bwd": 21, "fwd_kvcache": 16}
+    extra = {"bwd": {"deterministic"}, "varlen_bwd": {"deterministic"}, "fwd_kvcache": {"block_table"}}
     for name, n in want.items():
-        assert len(inspect.signature(getattr(ext, name)).parameters) == n, name
+        params = inspect.signature(getattr(ext, name)).parameters.values()
+        positional = [p for p in params if p.kind == inspect.Parameter.POSITIONAL_OR_KEYWORD]
+        assert len(positional) == n and all(p.default is inspect.Parameter.empty for p in positional), name
+        # what goes beyond this version of the reference is keyword-only and optional
+        kw_only = {p.name for p in params if p.kind == inspect.Parameter.KEYWORD_ONLY}
+        assert kw_only == extra.get(name, set()), name
+        assert all(p.default is not inspect.Parameter.empty for p in params if p.kind == inspect.Parameter.KEYWORD_ONLY)
 
 
 def test_shim_raises_runtime_error_like_torch_check():
