@@ -302,9 +302,21 @@ def measure_decode(R, steps, warmup):
 
     e2e()
     ms_e2e = statistics.median(timed_repeats(R, e2e, steps, min_repeats=3, target_ms=200.0))
+    # the caller path: host time to enqueue one step, eagerly and as a replayed CUDA graph of the same step
+    from flash_attention_b200.generation import DecodeGraphs, InferenceParams, host_time_per_call_us
+
+    params = InferenceParams(max_seqlen=cap, max_batch_size=B, lengths_per_sample=lens.clone())
+    graphs = DecodeGraphs(lambda p, q_, kn_, vn_: fa.flash_attn_with_kvcache(
+        q_, kc, vc, kn_, vn_, cos, sin, p.lengths_per_sample, causal=True, rotary_interleaved=False), params)
+    graphs.run(q, kn, vn, seqlen=lens)
+    caller = {"host_us_per_step_eager": host_time_per_call_us(step, 100),
+              "host_us_per_step_graph": host_time_per_call_us(lambda: graphs.run(q, kn, vn, seqlen=lens), 100),
+              "ms_per_step_graph": statistics.median(timed_repeats(R, lambda: graphs.run(q, kn, vn, seqlen=lens), steps,
+                                                                   min_repeats=3, target_ms=200.0))}
+    graphs.release()
     pk = peaks()
     res = {
-        "value": gbs, "unit": "GB/s", "ms_per_step": ms, "repeats": len(per_step),
+        "value": gbs, "unit": "GB/s", "ms_per_step": ms, "repeats": len(per_step), "caller_path": caller,
         "config": {"workload": "decode_b64_hq32_hk8_d128_cap32768", "batch_per_gpu": B, "cache_capacity": cap,
                    "cache_seqlens": "uniform [1024, 32767]", "new_tokens": 1, "rotary": "neox, dim 128, base 10000",
                    "l2": "8 GiB cache per GPU, larger than L2", "bytes_model": "sum_b (L_b + 1) * 8 * 128 * 2 B * 2"},
@@ -399,7 +411,7 @@ def measure_ring(R, steps, warmup, single_gpu_too=True):
     res = {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOPS/s", "ms_per_step": ms, "n_gpus": world, "scaling": "strong",
            "repeats": len(per_step),
            "config": {"workload": "ring_gqa_b1_s32768_h32_hk8_d128_causal", "rows_per_gpu": S_loc, "layout": "zigzag",
-                      "exchange": "K/V blocks by NCCL send/recv into local buffers; fp32 dK/dV accumulators travel in the backward"}}
+                      "exchange": "K/V blocks by NCCL send/recv into local buffers; fp32 dK/dV partials stay local, one reduce-scatter at the end of the backward"}}
     if single is not None or R.rank != 0:
         base = torch.tensor([single["value"] if single else 0.0], device=dev, dtype=torch.float64)
         if R.dist is not None:

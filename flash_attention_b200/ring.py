@@ -333,8 +333,9 @@ def ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group=Non
         gk_all, gv_all = g[src, 0], g[src, 1]
         if fast:
             qs, ks, cz = _causal_zigzag_plan(r, src, S_loc // 2)
-            dq[:, qs] += block_ops.bwd(dout[:, qs], q[:, qs], kc[:, ks], vc[:, ks], out[:, qs], lse[:, :, qs], gk_all[:, ks],
-                                       gv_all[:, ks], scale, (-1, 0) if cz else (-1, -1), 0).float()
+            # fp32 += 16-bit in one pass over dq
+            dq[:, qs].add_(block_ops.bwd(dout[:, qs], q[:, qs], kc[:, ks], vc[:, ks], out[:, qs], lse[:, :, qs], gk_all[:, ks],
+                                         gv_all[:, ks], scale, (-1, 0) if cz else (-1, -1), 0))
         else:
             theirs = layout_chunks(layout, src, P, S_loc)
             for qi, (qg, qn) in enumerate(mine):
@@ -346,8 +347,8 @@ def ring_backward(dout, q, k, v, out, lse, scale, causal, window_size, group=Non
                     whole = kn == S_loc or B == 1
                     gk = gk_all[:, ks] if whole else gk_all[:, ks].contiguous()
                     gv = gv_all[:, ks] if whole else gv_all[:, ks].contiguous()
-                    dq[:, qs] += block_ops.bwd(dout[:, qs], q[:, qs], kc[:, ks], vc[:, ks], out[:, qs], lse[:, :, qs], gk, gv,
-                                               scale, window, qg - kg).float()
+                    dq[:, qs].add_(block_ops.bwd(dout[:, qs], q[:, qs], kc[:, ks], vc[:, ks], out[:, qs], lse[:, :, qs], gk, gv,
+                                                 scale, window, qg - kg))
                     if not whole:
                         gk_all[:, ks] = gk
                         gv_all[:, ks] = gv

@@ -104,3 +104,43 @@ def test_noalloc_refuses_what_does_not_fit():
     # a windowed call is not the decode shape this entry point covers
     a.num_splits, a.window_left = 2, 5
     assert lib.fa_fwd_kvcache_noalloc(ctypes.byref(a), stream) == 1
+
+
+def test_noalloc_mostly_empty_splits_over_a_dirtied_buffer():
+    """The shared buffer is never cleared between calls.  First call: large values everywhere (scores far
+    from zero, every split in use).  Second call: same shape and split count, but sequences far shorter
+    than the cache, so most splits see no key at all and must contribute nothing, whatever the first call
+    left in their slots -- also when the buffer held infinities and NaNs."""
+    from flash_attention_b200 import _lib
+
+    lib = _lib.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    B, cap, H, Hk, D, dtype, splits = 4, 8192, 8, 8, 128, torch.bfloat16, 16
+    q, kc, vc, kn, vn, cos, sin, lens = _problem(21, B, cap, H, Hk, D, dtype)
+
+    def call(entry, q_, kc_, vc_, lens_):
+        kc_i, vc_i = kc_.clone(), vc_.clone()
+        out = torch.empty((B, 1, H, D), dtype=dtype, device="cuda")
+        lse = torch.empty((B, H, 1), dtype=torch.float32, device="cuda")
+        a = _args(_lib, q_, kc_i, vc_i, kn, vn, cos, sin, lens_, out, lse, splits)
+        keep = None
+        if entry == "fa_fwd_kvcache":
+            lb, ob = ctypes.c_int64(0), ctypes.c_int64(0)
+            assert lib.fa_kvcache_plan(ctypes.byref(a), 0, ctypes.byref(lb), ctypes.byref(ob)) == splits
+            # the caller-provided workspaces are poisoned on purpose: the same rule must hold for them
+            keep = (torch.full((lb.value // 4,), float("nan"), dtype=torch.float32, device="cuda"),
+                    torch.full((ob.value // 4,), float("inf"), dtype=torch.float32, device="cuda"))
+            a.lse_accum, a.out_accum = keep[0].data_ptr(), keep[1].data_ptr()
+        assert getattr(lib, entry)(ctypes.byref(a), stream) == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        return out, lse
+
+    full = torch.full((B,), cap - 1, dtype=torch.int32, device="cuda")
+    call("fa_fwd_kvcache_noalloc", q * 30, kc * 30, vc * 1000, full)  # dirties every slot with large numbers
+    short = torch.tensor([0, 1, 63, 700], dtype=torch.int32, device="cuda")  # 15 or 16 of the 16 splits are empty
+    o1, l1 = call("fa_fwd_kvcache_noalloc", q, kc, vc, short)
+    o0, l0 = call("fa_fwd_kvcache", q, kc, vc, short)
+    assert torch.isfinite(o1).all() and torch.isfinite(l1).all()
+    assert torch.isfinite(o0).all() and torch.isfinite(l0).all()
+    assert (o0.float() - o1.float()).abs().max().item() <= 1e-3 and (l0 - l1).abs().max().item() <= 1e-3
+    assert lib.fa_device_status() == 0
