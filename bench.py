@@ -259,18 +259,19 @@ def run_reference(args, wl):
 
 
 # ------------------------------------------------------------------------------------------------ decode
-def measure_decode(R, steps, warmup):
+def measure_decode(R, steps, warmup, B=64, cap=32768, caller_path=True):
     """KV-cache decode step: batch 64 (per GPU), 32 query heads, 8 KV heads, head_dim 128, bf16 cache of
-    capacity 32768 filled N(0,1), cache_seqlens uniform in [1024, 32767], one new token appended
-    in-kernel with NeoX rotary.  GB/s over the K and V rows actually attended to."""
+    capacity 32768 filled N(0,1), cache_seqlens uniform in [capacity / 32, capacity), one new token appended
+    in-kernel with NeoX rotary.  GB/s over the K and V rows actually attended to.  (B, cap) = (8, 8192) is
+    the same kernel on 0.27 GB of cache, for profiler captures.)"""
     import flash_attention_b200 as fa
 
     dev = R.dev
-    B, cap, H, Hk, D = 64, 32768, 32, 8, 128
+    H, Hk, D = 32, 8, 128
     g = torch.Generator(device=dev).manual_seed(4 + R.rank)
     kc = torch.randn(B, cap, Hk, D, device=dev, dtype=torch.bfloat16, generator=g)
     vc = torch.randn(B, cap, Hk, D, device=dev, dtype=torch.bfloat16, generator=g)
-    lens = torch.randint(1024, 32768, (B,), device=dev, generator=g).to(torch.int32)
+    lens = torch.randint(cap // 32, cap, (B,), device=dev, generator=g).to(torch.int32)
     q = torch.randn(B, 1, H, D, device=dev, dtype=torch.bfloat16, generator=g)
     kn = torch.randn(B, 1, Hk, D, device=dev, dtype=torch.bfloat16, generator=g)
     vn = torch.randn(B, 1, Hk, D, device=dev, dtype=torch.bfloat16, generator=g)
@@ -303,23 +304,27 @@ def measure_decode(R, steps, warmup):
     e2e()
     ms_e2e = statistics.median(timed_repeats(R, e2e, steps, min_repeats=3, target_ms=200.0))
     # the caller path: host time to enqueue one step, eagerly and as a replayed CUDA graph of the same step
-    from flash_attention_b200.generation import DecodeGraphs, InferenceParams, host_time_per_call_us
+    caller = None
+    if caller_path:
+        from flash_attention_b200.generation import DecodeGraphs, InferenceParams, host_time_per_call_us
 
-    params = InferenceParams(max_seqlen=cap, max_batch_size=B, lengths_per_sample=lens.clone())
-    graphs = DecodeGraphs(lambda p, q_, kn_, vn_: fa.flash_attn_with_kvcache(
-        q_, kc, vc, kn_, vn_, cos, sin, p.lengths_per_sample, causal=True, rotary_interleaved=False), params)
-    graphs.run(q, kn, vn, seqlen=lens)
-    caller = {"host_us_per_step_eager": host_time_per_call_us(step, 100),
-              "host_us_per_step_graph": host_time_per_call_us(lambda: graphs.run(q, kn, vn, seqlen=lens), 100),
-              "ms_per_step_graph": statistics.median(timed_repeats(R, lambda: graphs.run(q, kn, vn, seqlen=lens), steps,
-                                                                   min_repeats=3, target_ms=200.0))}
-    graphs.release()
+        params = InferenceParams(max_seqlen=cap, max_batch_size=B, lengths_per_sample=lens.clone())
+        graphs = DecodeGraphs(lambda p, q_, kn_, vn_: fa.flash_attn_with_kvcache(
+            q_, kc, vc, kn_, vn_, cos, sin, p.lengths_per_sample, causal=True, rotary_interleaved=False), params)
+        replay = lambda: graphs.run(q, kn, vn, seqlen=lens)  # noqa: E731
+        replay()
+        caller = {"host_us_per_step_eager": host_time_per_call_us(step, 100),
+                  "host_us_per_step_graph": host_time_per_call_us(replay, 100),
+                  "ms_per_step_graph": statistics.median(timed_repeats(R, replay, steps, min_repeats=3, target_ms=200.0))}
+        graphs.release()
     pk = peaks()
     res = {
         "value": gbs, "unit": "GB/s", "ms_per_step": ms, "repeats": len(per_step), "caller_path": caller,
-        "config": {"workload": "decode_b64_hq32_hk8_d128_cap32768", "batch_per_gpu": B, "cache_capacity": cap,
-                   "cache_seqlens": "uniform [1024, 32767]", "new_tokens": 1, "rotary": "neox, dim 128, base 10000",
-                   "l2": "8 GiB cache per GPU, larger than L2", "bytes_model": "sum_b (L_b + 1) * 8 * 128 * 2 B * 2"},
+        "config": {"workload": "decode_b%d_hq32_hk8_d128_cap%d" % (B, cap), "batch_per_gpu": B, "cache_capacity": cap,
+                   "cache_seqlens": "uniform [%d, %d]" % (cap // 32, cap - 1), "new_tokens": 1,
+                   "rotary": "neox, dim 128, base 10000",
+                   "l2": "%.2f GiB of cache per GPU, larger than L2" % (2.0 * B * cap * Hk * D * 2 / 2 ** 30),
+                   "bytes_model": "sum_b (L_b + 1) * 8 * 128 * 2 B * 2"},
         "roofline": {"bound": "hbm", "kernel": "decode_kernel (+ combine_kernel)", "achieved": gbs / R.world,
                      "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / R.world / pk["hbm_gbs"], "traffic": None,
                      "peak_source": pk["source"]},
@@ -337,14 +342,15 @@ def run_decode(args):
     from flash_attention_b200 import _lib
 
     R = Ranks()
-    res = measure_decode(R, args.steps, args.warmup)
+    small = args.workload == "decode_b8_cap8192"
+    res = measure_decode(R, args.steps, args.warmup, *((8, 8192) if small else (64, 32768)), caller_path=not args.no_also)
     status = _lib.lib().fa_device_status()
     if R.rank == 0:
         print(json.dumps({
             "metric": "decode KV-cache GB/s (bf16, d128, split-KV)", "value": res["value"], "unit": "GB/s", "n_gpus": R.world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": res["ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": res["config"],
-            "roofline": res["roofline"], "cpu_baseline": None, "e2e": res["e2e"],
+            "roofline": res["roofline"], "cpu_baseline": None, "e2e": res["e2e"], "caller_path": res["caller_path"],
             "gpu_launches": args.steps * 2, "clocks": res["clocks"], "device_status": status,
         }))
     R.close()
@@ -691,7 +697,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-also", action="store_true", help="skip the decode and ring measurements of the default workload")
+    ap.add_argument("--no-also", action="store_true", help="skip the decode and ring measurements of the default workload, and the caller-path part of the decode workload")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args, args.workload if args.workload in WORKLOADS else DEFAULT)
@@ -699,7 +705,7 @@ def main():
         return run_ring(args)
     if args.workload == "rotary":
         return run_rotary(args)
-    if args.workload == "decode":
+    if args.workload in ("decode", "decode_b8_cap8192"):
         return run_decode(args)
     return run_train(args, args.workload)
 
