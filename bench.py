@@ -79,12 +79,14 @@ class ClockSampler:
     def __init__(self, index):
         self.index = index
         self.rows = []
+        self.stamps = []
+        self.windows = []  # (start, end) wall-clock times of the timed regions
         self.proc = None
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -95,6 +97,10 @@ class ClockSampler:
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([x.strip() for x in line.split(",")])
+            self.stamps.append(time.time())
+
+    def mark(self, t0, t1):
+        self.windows.append((t0, t1))
 
     def __exit__(self, *a):
         if self.proc is not None:
@@ -107,7 +113,11 @@ class ClockSampler:
     def summary(self):
         sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        # a sample counts when it was taken while a timed region ran (nvidia-smi reports ~10 ms after it reads);
+        # with no region marked, every sample counts
+        inside = [r for r, t in zip(self.rows, self.stamps)
+                  if not self.windows or any(a <= t - 0.01 <= b + 0.02 for a, b in self.windows)]
+        for r in inside:
             if len(r) < 6:
                 continue
             try:
@@ -163,20 +173,28 @@ class Ranks:
             self.dist.destroy_process_group()
 
 
-def timed_repeats(R, fn, steps, min_repeats=5, target_ms=250.0, max_repeats=40):
+def timed_repeats(R, fn, steps, min_repeats=5, target_ms=250.0, max_repeats=40, gap_s=0.0, clk=None):
     """Times `steps` calls of fn as one region, several times.  Each region is bracketed by a barrier +
     synchronize on both sides, timed with CUDA events on the launching stream, and its time is the max
     over ranks.  The number of repeats (the same on all ranks) is chosen from the first region so that
-    the whole measurement lasts about target_ms.  Returns the list of per-step times in ms."""
+    the regions together last about target_ms.  gap_s > 0 leaves the GPU idle for that long before every
+    region, so that each region starts from the idle power state (how a burst peak is measured); gap_s = 0
+    runs them back to back (sustained, under the power cap).  clk: a ClockSampler that is told when each
+    region ran.  Returns the list of per-step times in ms."""
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     def region():
+        if gap_s > 0:
+            time.sleep(gap_s)
         R.barrier()
+        t0 = time.time()
         ev0.record()
         for _ in range(steps):
             fn()
         ev1.record()
         R.barrier()
+        if clk is not None:
+            clk.mark(t0, time.time())
         return R.max_over_ranks(ev0.elapsed_time(ev1))
 
     first = region()
@@ -548,22 +566,28 @@ def run_train(args, wl):
     warm = max(3, args.warmup)
     for _ in range(warm):
         step(inputs, dout)
-    # ---- timed region: K steps, device timed, max over ranks; repeated, median reported
+    # ---- timed region: K steps, device timed, max over ranks; repeated, median reported.  The GPU idles GAP_S before
+    # every region: K steps of this workload are a burst of tens of milliseconds, and the denominator they are compared
+    # with (the measured burst peak) was taken the same way.  The same regions back to back, where the 1 kW power cap
+    # lowers the SM clock after ~0.1 s, are reported beside them as "sustained".
+    GAP_S = 0.4
     with ClockSampler(R.local) as clk:
-        per_step = timed_repeats(R, lambda: step(inputs, dout), args.steps)
+        per_step = timed_repeats(R, lambda: step(inputs, dout), args.steps, min_repeats=7, max_repeats=12, gap_s=GAP_S, clk=clk)
     ms_step = statistics.median(per_step)
     value = world * f_step / (ms_step * 1e-3) / 1e12
     clocks = clk.summary()
+    with ClockSampler(R.local) as clk_s:
+        ms_sustained = statistics.median(timed_repeats(R, lambda: step(inputs, dout), args.steps, target_ms=400.0, clk=clk_s))
 
     # ---- forward and backward timed separately (the kernels behind the roofline numbers)
     def forward_only():
         with torch.no_grad():
             forward(inputs)
 
-    ms_fwd = statistics.median(timed_repeats(R, forward_only, args.steps, target_ms=150.0))
+    ms_fwd = statistics.median(timed_repeats(R, forward_only, args.steps, max_repeats=7, gap_s=GAP_S))
     out = forward(inputs)
     ms_bwd = statistics.median(timed_repeats(R, lambda: torch.autograd.grad(out, inputs, dout, retain_graph=True), args.steps,
-                                             target_ms=150.0))
+                                             max_repeats=7, gap_s=GAP_S))
     del out
     pk = peaks()
     tf_fwd = f_fwd / (ms_fwd * 1e-3) / 1e12
@@ -580,7 +604,13 @@ def run_train(args, wl):
                 "forward": {"kernel": "fwd_tc_kernel", "achieved": tf_fwd, "frac": tf_fwd / pk["tflops_burst"],
                             "frac_of_sustained": tf_fwd / pk["tflops_sustained"]},
                 "step": {"achieved": value / world, "frac": value / world / pk["tflops_burst"]},
-                "frac_of_sustained": tf_bwd / pk["tflops_sustained"]}
+                "sustained": {"step_tflops": f_step / (ms_sustained * 1e-3) / 1e12, "ms_per_step": ms_sustained,
+                              "peak": pk["tflops_sustained"],
+                              "frac": f_step / (ms_sustained * 1e-3) / 1e12 / pk["tflops_sustained"],
+                              "clocks": clk_s.summary(),
+                              "note": "the same K-step regions back to back for >= 0.4 s, under the power cap; "
+                                      "against the measured sustained peak"},
+                "timing": "regions of K steps, GPU idle %.1f s before each, median of >= 7; against the measured burst peak" % GAP_S}
 
     # ---- end to end: every step copies its inputs from pinned host memory, computes, and copies its RESULT (out and
     # the gradient of every input) back to pinned host memory.  As a training loop would, the three stages run on
@@ -674,7 +704,8 @@ def run_train(args, wl):
                        "flop_model": "fwd 4*B*S^2*H*D%s, bwd 2.5x" % ("/2" if causal else ""),
                        "parallelism": "independent (batch x head) units per GPU, no communication"},
             "timing": {"repeats": len(per_step), "ms_per_step_min": min(per_step), "ms_per_step_max": max(per_step),
-                       "ms_per_step_median": ms_step, "ms_times_sm_mhz": ms_step * mhz if mhz else None},
+                       "ms_per_step_median": ms_step, "ms_times_sm_mhz": ms_step * mhz if mhz else None,
+                       "idle_s_before_each_region": GAP_S, "ms_per_step_back_to_back": ms_sustained},
             "fwd_tflops": tf_fwd, "bwd_tflops": tf_bwd, "ms_fwd": ms_fwd, "ms_bwd": ms_bwd,
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_val, "unit": "TFLOPS/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
