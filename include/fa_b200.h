@@ -22,8 +22,9 @@
  *     with a negative window meaning "unbounded on that side" (csrc/flash_attn/src/softmax.h:142-179).
  *     `causal` is window_right = 0.
  *   - every function enqueues work on `stream` and returns without synchronising; 0 = success,
- *     otherwise fa_last_error() describes the failure (the shim raises RuntimeError, mirroring
- *     TORCH_CHECK in the reference).
+ *     1 = invalid arguments, 2 = a CUDA call failed, 3 = refused because an earlier kernel gave up on
+ *     a bounded wait (see fa_device_status); fa_last_error() describes the failure (the shim raises
+ *     RuntimeError, mirroring TORCH_CHECK in the reference).
  */
 #ifndef FA_B200_H_
 #define FA_B200_H_
