@@ -442,6 +442,19 @@ def measure_ring(R, steps, warmup, single_gpu_too=True):
             R.dist.broadcast(base, src=0)
         res["single_gpu_value"] = base.item()
         res["speedup_over_single_gpu"] = res["value"] / base.item() if base.item() > 0 else None
+    if world > 1:
+        # the same kernels in the same order with nothing exchanged: what is left of a step is exchange that the
+        # kernels did not hide (send/recv of K/V, the reduce-scatter of dK/dV)
+        try:
+            from flash_attention_b200 import ring
+
+            with ring.kernels_only():
+                step()
+                ms_k = statistics.median(timed_repeats(R, step, max(1, min(steps, 10)), min_repeats=3, target_ms=200.0))
+            res["kernels_only_ms_per_step"] = ms_k
+            res["exposed_exchange_share"] = max(0.0, 1.0 - ms_k / ms)
+        except Exception as e:  # a diagnostic: must not cost the number above
+            res["kernels_only_error"] = repr(e)[:200]
     return res
 
 
