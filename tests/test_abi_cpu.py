@@ -166,3 +166,55 @@ def test_per_device_setup_runs_once_per_device(lib):
     assert lib.fa_selftest_device_once(arr, len(devs), out) == 0
     # ordinals outside the 64-entry table are configured on every call rather than never
     assert list(out) == [1, 0, 1, 0, 0, 1, 1, 0, 1, 1, 1, 1]
+
+
+def test_paged_cache_arguments_are_validated_before_launch(lib):
+    """block_table rules of FaKvcacheArgs / FaFwdArgs, checked on the host (fa_kvcache_plan launches nothing)."""
+    from flash_attention_b200 import _lib
+
+    a = _lib.FaKvcacheArgs()
+    a.batch, a.batch_cache, a.seqlen_q, a.seqlen_cache, a.heads, a.heads_k, a.head_dim, a.dtype = 2, 9, 1, 1024, 8, 2, 128, 1
+    table = (ctypes.c_int32 * 8)(*range(8))
+    a.block_table = ctypes.cast(table, ctypes.c_void_p)
+    a.block_table_stride, a.page_block_size = 4, 256
+    assert lib.fa_kvcache_plan(ctypes.byref(a), 148, None, None) >= 1  # 4 pages of 256 rows per sequence
+    a.page_block_size = 96
+    assert lib.fa_kvcache_plan(ctypes.byref(a), 148, None, None) == -1
+    assert b"divisible by 64" in lib.fa_last_error()
+    a.page_block_size, a.seqlen_cache = 256, 2048  # more pages than a row of the table holds
+    assert lib.fa_kvcache_plan(ctypes.byref(a), 148, None, None) == -1
+    assert b"block_table" in lib.fa_last_error()
+    a.seqlen_cache = 1000  # not whole pages
+    assert lib.fa_kvcache_plan(ctypes.byref(a), 148, None, None) == -1
+    a.seqlen_cache = 1024
+    idx = (ctypes.c_int32 * 2)(0, 1)
+    a.cache_batch_idx = ctypes.cast(idx, ctypes.c_void_p)
+    assert lib.fa_kvcache_plan(ctypes.byref(a), 148, None, None) == -1
+    assert b"cache_batch_idx" in lib.fa_last_error()
+    # a paged pool may hold fewer pages than there are sequences x pages (sharing) or more: batch_cache is not compared
+    # with batch
+    a.cache_batch_idx = None
+    a.batch_cache = 1
+    assert lib.fa_kvcache_plan(ctypes.byref(a), 148, None, None) >= 1
+    # the plan (split count, workspace sizes) of a paged call is that of the contiguous call of the same capacity
+    lb, ob, lb2, ob2 = (ctypes.c_int64(0) for _ in range(4))
+    paged = lib.fa_kvcache_plan(ctypes.byref(a), 148, ctypes.byref(lb), ctypes.byref(ob))
+    a.block_table, a.block_table_stride, a.page_block_size, a.batch_cache = None, 0, 0, 2
+    flat = lib.fa_kvcache_plan(ctypes.byref(a), 148, ctypes.byref(lb2), ctypes.byref(ob2))
+    assert paged == flat and lb.value == lb2.value and ob.value == ob2.value
+
+    f = _lib.FaFwdArgs()
+    f.batch, f.seqlen_q, f.seqlen_k, f.heads, f.heads_k, f.head_dim, f.dtype = 1, 8, 512, 4, 4, 64, 1
+    buf = ctypes.create_string_buffer(4096 + 64)
+    base = (ctypes.addressof(buf) + 15) & ~15
+    for t in (f.q, f.k, f.v, f.out):
+        t.ptr, t.stride_b, t.stride_s, t.stride_h = base, 0, 64, 64
+    f.softmax_lse = base
+    f.block_table = ctypes.cast(table, ctypes.c_void_p)
+    f.block_table_stride, f.page_block_size = 4, 100
+    assert lib.fa_fwd(ctypes.byref(f), None) == 1 and b"divisible by 64" in lib.fa_last_error()
+    f.page_block_size = 64  # 4 pages x 64 rows < 512 keys
+    assert lib.fa_fwd(ctypes.byref(f), None) == 1 and b"cover seqlen_k" in lib.fa_last_error()
+    f.block_table_stride = 8
+    f.kv_batch_idx = ctypes.cast(idx, ctypes.c_void_p)
+    assert lib.fa_fwd(ctypes.byref(f), None) == 1 and b"paged" in lib.fa_last_error()
