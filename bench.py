@@ -42,7 +42,7 @@ METRIC = "attention fwd+bwd TFLOPS/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the backward kernels of one step, from ncu captures of these
 # kernels on these workloads (d128: dK/dV kernel + dQ kernel; d256: the three passes of the wide kernel)
-NCU_DRAM_BYTES_PER_BACKWARD = {"train_b16_s2048_h16_d128_causal": 1.4427e9, "train_b16_s2048_h8_d256": 1.8321e9}
+NCU_DRAM_BYTES_PER_BACKWARD = {"train_b16_s2048_h16_d128_causal": 1.4427e9, "train_b16_s2048_h8_d256": 1.8399e9}
 
 WORKLOADS = {
     # name: (batch, seqlen, heads, heads_k, head_dim, causal, dtype)
