@@ -277,6 +277,62 @@ def run_reference(args, wl):
 
 
 # ------------------------------------------------------------------------------------------------ decode
+def measure_other_shapes(R, steps):
+    """The other BASELINE shapes in the same run, briefly: fwd+bwd, forward and backward TFLOP/s per GPU for every
+    workload of WORKLOADS besides the default one, and for the packed variable-length case (lengths ~ U[128, 4096]
+    until 65536 tokens, seed 3, 16 heads, head dim 128, fp16, causal).  Three regions of `steps` steps each, every
+    region started from an idle GPU; the median is reported."""
+    import flash_attention_b200 as fa
+
+    dev = R.dev
+    res = {}
+
+    def timed(fn):
+        fn()
+        return statistics.median(timed_repeats(R, fn, steps, min_repeats=3, max_repeats=3, gap_s=0.2))
+
+    def fwd_bwd(name, forward, inputs, dout, f_fwd):
+        def fwd_only():
+            with torch.no_grad():
+                forward()
+
+        ms_f = timed(fwd_only)
+        out = forward()
+        ms_b = timed(lambda: torch.autograd.grad(out, inputs, dout, retain_graph=True))
+        del out
+        # fwd_bwd: from the forward and the backward timed separately
+        res[name] = {"fwd_bwd_tflops": 3.5 * f_fwd / ((ms_f + ms_b) * 1e-3) / 1e12, "fwd_tflops": f_fwd / (ms_f * 1e-3) / 1e12,
+                     "bwd_tflops": 2.5 * f_fwd / (ms_b * 1e-3) / 1e12, "ms_fwd": ms_f, "ms_bwd": ms_b}
+
+    for wl, (B, S, H, Hk, D, causal, dtype) in WORKLOADS.items():
+        if wl == DEFAULT:
+            continue
+        g = torch.Generator(device=dev).manual_seed(11 + R.rank)
+        q = torch.randn(B, S, H, D, device=dev, dtype=dtype, generator=g).requires_grad_(True)
+        k = torch.randn(B, S, Hk, D, device=dev, dtype=dtype, generator=g).requires_grad_(True)
+        v = torch.randn(B, S, Hk, D, device=dev, dtype=dtype, generator=g).requires_grad_(True)
+        do = torch.randn(B, S, H, D, device=dev, dtype=dtype, generator=g)
+        fwd_bwd(wl, lambda: fa.flash_attn_func(q, k, v, causal=causal), (q, k, v), do, fwd_flops(B, S, H, D, causal))
+        del q, k, v, do
+    H, D = 16, 128
+    gl = torch.Generator().manual_seed(3)
+    lens, total = [], 0
+    while total < 65536:
+        n = min(int(torch.randint(128, 4097, (1,), generator=gl)), 65536 - total)
+        lens.append(n)
+        total += n
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(12 + R.rank)
+    q, k, v = (torch.randn(total, H, D, device=dev, dtype=torch.float16, generator=g).requires_grad_(True) for _ in range(3))
+    do = torch.randn(total, H, D, device=dev, dtype=torch.float16, generator=g)
+    f_fwd = sum(4.0 * n * n * H * D / 2.0 for n in lens)
+    fwd_bwd("varlen_fp16_%dseqs_65536tok_h16_d128_causal" % len(lens),
+            lambda: fa.flash_attn_varlen_func(q, k, v, cu, cu, max(lens), max(lens), causal=True), (q, k, v), do, f_fwd)
+    del q, k, v, do
+    torch.cuda.empty_cache()
+    return res
+
+
 def measure_decode(R, steps, warmup, B=64, cap=32768, caller_path=True):
     """KV-cache decode step: batch 64 (per GPU), 32 query heads, 8 KV heads, head_dim 128, bf16 cache of
     capacity 32768 filled N(0,1), cache_seqlens uniform in [capacity / 32, capacity), one new token appended
@@ -683,6 +739,7 @@ def run_train(args, wl):
     launches = args.steps * (5 if wide else 4)
     if wl == DEFAULT and not args.no_also:
         for name, fn in (("decode", lambda: measure_decode(R, max(3, min(args.steps, 20)), 3)),
+                         ("shapes", lambda: measure_other_shapes(R, max(2, min(args.steps, 10)))),
                          ("ring", lambda: measure_ring(R, max(2, min(args.steps, 5)), 2))):
             try:
                 also[name] = fn()
